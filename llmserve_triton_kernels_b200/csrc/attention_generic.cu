@@ -46,7 +46,8 @@ __global__ void __launch_bounds__(WARPS * 32) attention_rows_kernel(const RowsAr
     float acc[ACC];
 #pragma unroll
     for (int i = 0; i < ACC; ++i) acc[i] = 0.f;
-    float m = -INFINITY, l = 0.f;
+    // a sink stands for a key of score sinks[h] and no value: the running maximum and sum start from it
+    float m = a.sinks ? a.sinks[h] : -INFINITY, l = a.sinks ? 1.f : 0.f;
 
     for (int c = (lo / 32) * 32; c <= pos; c += 32) {
         const int j = c + lane;
@@ -82,10 +83,15 @@ __global__ void __launch_bounds__(WARPS * 32) attention_rows_kernel(const RowsAr
     }
     const float inv = 1.f / l;
     T* op = a.out + (long long)t * a.out_token + (long long)h * a.out_head;
+    const float* gp = a.gate ? a.gate + (long long)t * a.gate_token + (long long)h * dv : nullptr;
 #pragma unroll
     for (int i = 0; i < ACC; ++i) {
         const int d = lane + 32 * i;
-        if (d < dv) op[d] = from_float<T>(acc[i] * inv);
+        if (d < dv) {
+            float y = acc[i] * inv;
+            if (gp) y *= 1.f / (1.f + expf(-gp[d]));
+            op[d] = from_float<T>(y);
+        }
     }
 }
 
@@ -108,7 +114,8 @@ LLM_EXPORT int llm_attention_rows(const void* q0, long long q0_token, long long 
                                   const void* values, long long v_page, long long v_head, long long v_token, int dv, int dtype,
                                   const int* page_table, int table_width, const int* token_request, const int* cu_tokens,
                                   const int* ctx_lens, const float* slopes, int n_tokens, int H, int KV, int page_size,
-                                  int window, float scale, cudaStream_t stream) {
+                                  int window, float scale, const float* sinks, const float* gate, long long gate_token,
+                                  cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (d0 <= 0 || d1 < 0 || d0 + d1 > MAX_DK || dv <= 0 || dv > MAX_DV || H <= 0 || KV <= 0 || H % KV || page_size <= 0 ||
         table_width <= 0 || (d1 > 0 && q1 == nullptr))
@@ -127,6 +134,7 @@ LLM_EXPORT int llm_attention_rows(const void* q0, long long q0_token, long long 
         a.table_width = table_width; a.n_tokens = n_tokens; a.H = H; a.KV = KV; a.page_size = page_size; a.window = window;
         a.scale = scale;
         a.key_part = 0; a.keys1 = nullptr; a.k1_token = 0; a.fresh_d0 = 0; a.stats = nullptr;
+        a.sinks = sinks; a.gate = gate; a.gate_token = gate_token;
     };
     if (dtype == LLM_F32) {
         RowsArgs<float> a;
@@ -154,5 +162,5 @@ LLM_EXPORT int llm_attention_generic(const void* q, int q_stride, void* out, int
     const void* values = (const char*)pool + (size_t)KV * head * element;
     return llm_attention_rows(q, q_stride, D, D, nullptr, 0, 0, 0, out, out_stride, D, pool, page, head, D, values, page, head,
                               D, D, dtype, page_table, table_width, token_request, cu_tokens, ctx_lens, nullptr, n_tokens, H,
-                              KV, page_size, window, scale, stream);
+                              KV, page_size, window, scale, nullptr, nullptr, 0, stream);
 }

@@ -32,5 +32,11 @@ struct RowsArgs {
     // [n_tokens, H, 2] (or null): the row's maximum score (times log2 e) and the sum of its exponentials, for a merge of two parts; a
     // row that saw no key says (-inf, 0) and its output is not to be read
     float* stats;
+    // per query head (or null): one more term exp(sinks[h]) in the softmax's denominator, with no key and no value; it is
+    // not scaled and counts once
+    const float* sinks;
+    // [n_tokens, gate_token] float32 (or null): the output of head h, lane d is multiplied by sigmoid(gate[t, h * dv + d])
+    const float* gate;
+    long long gate_token;
 };
 

@@ -162,6 +162,16 @@ attention_rows_mma_kernel(const RowsArgs<bf16> a, int splits, float* __restrict_
         warp_hi = a.key_part == 1 ? min(p0, first_pos - 1) : p0;
     }
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    if (a.sinks && split == 0) {
+        // a sink stands for a key of score sinks[h] (not scaled) without a value; the first split counts it, once a row
+        // (a row's sum is kept in four lanes' shares until the end: the share of the first takes it)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            const int R = min(row0 + warp * 16 + (lane >> 2) + 8 * e, rows_total - 1);
+            m[e] = a.sinks[kvh * group + R % group] * LOG2E;
+            l[e] = (lane & 3) == 0 ? 1.f : 0.f;
+        }
+    }
     float o[DV_MAX / 8][4];
 #pragma unroll
     for (int i = 0; i < DV_MAX / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
@@ -274,11 +284,17 @@ attention_rows_mma_kernel(const RowsArgs<bf16> a, int splits, float* __restrict_
                 a.stats[((size_t)t * a.H + h) * 2 + 1] = l[e];
             }
             bf16* op = a.out + (long long)t * a.out_token + (long long)h * a.out_head;
+            const float* gp = a.gate ? a.gate + (long long)t * a.gate_token + (long long)h * dv : nullptr;
 #pragma unroll
             for (int i = 0; i < DV_MAX / 8; ++i)
                 if (i * 8 < dv) {
                     const int col = i * 8 + (lane & 3) * 2;
-                    *reinterpret_cast<__nv_bfloat162*>(op + col) = __floats2bfloat162_rn(o[i][2 * e] * inv, o[i][2 * e + 1] * inv);
+                    float y0 = o[i][2 * e] * inv, y1 = o[i][2 * e + 1] * inv;
+                    if (gp) {
+                        y0 *= 1.f / (1.f + __expf(-gp[col]));
+                        y1 *= 1.f / (1.f + __expf(-gp[col + 1]));
+                    }
+                    *reinterpret_cast<__nv_bfloat162*>(op + col) = __floats2bfloat162_rn(y0, y1);
                 }
         } else {
             const size_t slot = ((size_t)t * a.H + h) * splits + split;
@@ -300,7 +316,8 @@ attention_rows_mma_kernel(const RowsArgs<bf16> a, int splits, float* __restrict_
 // out[t, h] = sum_s exp(m_s - M) o_s / sum_s exp(m_s - M) l_s over the splits' partial results; one warp per (token, head)
 __global__ void __launch_bounds__(128)
 attention_rows_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, bf16* __restrict__ out,
-                            long long out_token, long long out_head, int n_tokens, int H, int dv, int splits) {
+                            long long out_token, long long out_head, int n_tokens, int H, int dv, int splits,
+                            const float* __restrict__ gate, long long gate_token) {
     const int lane = threadIdx.x & 31;
     const long long item = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
     pdl_trigger();
@@ -329,7 +346,11 @@ attention_rows_merge_kernel(const float* __restrict__ part_o, const float* __res
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
             const int d = d0 + lane + 32 * i;
-            if (d < dv) op[d] = __float2bfloat16_rn(acc[i] * inv);
+            if (d < dv) {
+                float y = acc[i] * inv;
+                if (gate) y *= 1.f / (1.f + __expf(-gate[(long long)t * gate_token + (long long)h * dv + d]));
+                op[d] = __float2bfloat16_rn(y);
+            }
         }
     }
 }
@@ -438,7 +459,8 @@ LLM_EXPORT int llm_attention_rows_mma(const void* q0, long long q0_token, long l
                                       const int* token_request, const int* cu_tokens, const int* ctx_lens, const float* slopes,
                                       int n_tokens, int requests, int max_query_len, int H, int KV, int page_size, int window,
                                       float scale, int splits, float* part_o, float* part_ml, int key_part, const void* keys1,
-                                      long long k1_token, int fresh_d0, float* stats, cudaStream_t stream) {
+                                      long long k1_token, int fresh_d0, float* stats, const float* sinks, const float* gate,
+                                      long long gate_token, cudaStream_t stream) {
     if (n_tokens <= 0 || requests <= 0) return 0;
     if (d0 <= 0 || d1 < 0 || dv <= 0 || H <= 0 || KV <= 0 || H % KV || page_size <= 0 || table_width <= 0 || splits < 1 ||
         max_query_len < 1 || (d1 > 0 && q1 == nullptr) || (splits > 1 && (part_o == nullptr || part_ml == nullptr)))
@@ -447,6 +469,8 @@ LLM_EXPORT int llm_attention_rows_mma(const void* q0, long long q0_token, long l
     auto aligned = [](const void* p) { return ((uintptr_t)p & 15) == 0; };
     if ((d0 & 15) || (d1 & 15) || (dv & 15) || dv > 256 || dk > 640) return LLM_ERR_UNSUPPORTED;
     if (key_part < 0 || key_part > 2 || (stats && splits != 1)) return LLM_ERR_BAD_ARGUMENT;
+    if ((sinks || gate) && (key_part != 0 || stats)) return LLM_ERR_BAD_ARGUMENT;  // a sink belongs to a whole softmax, not to a part of one
+    if (gate && (splits > 1 && out == nullptr)) return LLM_ERR_BAD_ARGUMENT;
     if (key_part == 2 && keys1 && ((fresh_d0 & 15) || fresh_d0 <= 0 || fresh_d0 >= dk || (k1_token & 7) || ((uintptr_t)keys1 & 15)))
         return LLM_ERR_UNSUPPORTED;
     if ((q0_token & 7) || (q0_head & 7) || (q1_token & 7) || (q1_head & 7) || (k_page & 7) || (k_head & 7) || (k_token & 7) ||
@@ -467,6 +491,7 @@ LLM_EXPORT int llm_attention_rows_mma(const void* q0, long long q0_token, long l
     a.scale = scale;
     a.key_part = key_part; a.keys1 = key_part == 2 ? (const bf16*)keys1 : nullptr; a.k1_token = k1_token; a.fresh_d0 = fresh_d0;
     a.stats = stats;
+    a.sinks = sinks; a.gate = gate; a.gate_token = gate_token;
     const bool alias = key_part != 2 && values == keys && v_page == k_page && v_head == k_head && v_token == k_token;
     auto smem_for = [&](int bn, int bm = 64) { return (size_t)(bm + 2 * bn) * (dk + PAD) * 2 + (alias ? 0 : (size_t)2 * bn * (dv + PAD) * 2); };
     const bool wide = smem_for(64) <= 160 * 1024;
@@ -491,7 +516,7 @@ LLM_EXPORT int llm_attention_rows_mma(const void* q0, long long q0_token, long l
     if (code != 0 || splits == 1 || out == nullptr) return code;  // no out: the partial results are what the caller wants
     const long long items = (long long)n_tokens * H;
     return launch_pdl(attention_rows_merge_kernel, dim3((unsigned)((items + 3) / 4)), dim3(128), 0, stream, (const float*)part_o,
-                      (const float*)part_ml, (bf16*)out, out_token, out_head, n_tokens, H, dv, splits);
+                      (const float*)part_ml, (bf16*)out, out_token, out_head, n_tokens, H, dv, splits, gate, gate_token);
 }
 
 // The partial results of llm_attention_rows_mma with splits > 1 and no out (part_o, part_ml), merged, multiplied per head

@@ -99,6 +99,8 @@ LLM_EXPORT int llm_gemm_simt(const void* x, int x_dtype, const void* w, int w_dt
         return launch<bf, bf, bf>(x, w, out, M, N, K, ldx, ldw, ldo, stream);
     if (x_dtype == LLM_BF16 && w_dtype == LLM_BF16 && out_dtype == LLM_F32)
         return launch<bf, bf, float>(x, w, out, M, N, K, ldx, ldw, ldo, stream);
+    if (x_dtype == LLM_F32 && w_dtype == LLM_BF16 && out_dtype == LLM_F32)  // an input that stays 32-bit against stored weights
+        return launch<float, bf, float>(x, w, out, M, N, K, ldx, ldw, ldo, stream);
     return LLM_ERR_BAD_ARGUMENT;
 }
 

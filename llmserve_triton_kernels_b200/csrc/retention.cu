@@ -253,11 +253,12 @@ retention_starts_kernel(const float* __restrict__ ends, float* __restrict__ star
 }
 
 // out[t, h, :] = o[t, h, :] / sqrt(mean(o[t, h, :]^2) + eps) * gate(g[t, h, :]), one warp per (token, head).
-// gate_kind: 0 sigmoid(g), 1 silu(g), -1 none.  eps < 0: no norm.
+// gate_kind: 0 sigmoid(g), 1 silu(g), -1 none.  eps < 0: no norm.  weight [V] (or null): the normed lanes times it, the
+// same for every head.
 template <typename TG, typename TO>
 __global__ void __launch_bounds__(128)
 head_norm_gate_kernel(const float* __restrict__ o, const TG* __restrict__ g, int ldg, TO* __restrict__ out, int rows, int heads,
-                      int V, float eps, int gate_kind) {
+                      int V, float eps, int gate_kind, const float* __restrict__ weight) {
     pdl_trigger();
     const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     pdl_wait();
@@ -270,6 +271,7 @@ head_norm_gate_kernel(const float* __restrict__ o, const TG* __restrict__ g, int
     const float scale = eps >= 0.f ? 1.f / sqrtf(ss / (float)V + eps) : 1.f;
     for (int i = lane; i < V; i += 32) {
         float y = src[i] * scale;
+        if (weight) y *= weight[i];
         if (gate_kind >= 0) {
             const float z = to_float(g[(size_t)t * ldg + (size_t)h * V + i]);
             const float s = 1.f / (1.f + expf(-z));
@@ -322,13 +324,13 @@ LLM_EXPORT int llm_retention_scan(const float* q, int ldq, const float* k, int l
 }
 
 LLM_EXPORT int llm_head_norm_gate(const float* o, const void* g, int g_dtype, int ldg, void* out, int out_dtype, int N, int heads,
-                                  int V, float eps, int gate_kind, cudaStream_t stream) {
+                                  int V, float eps, int gate_kind, const float* weight, cudaStream_t stream) {
     if (N <= 0) return 0;
     if (heads <= 0 || V <= 0 || (gate_kind >= 0 && !g)) return LLM_ERR_BAD_ARGUMENT;
     const int rows = N * heads;
     const dim3 grid((rows + 3) / 4), block(128);
     using bf = __nv_bfloat16;
-    auto go = [&](auto kernel, auto* gp, auto* op) { return launch_pdl(kernel, grid, block, 0, stream, o, gp, ldg, op, rows, heads, V, eps, gate_kind); };
+    auto go = [&](auto kernel, auto* gp, auto* op) { return launch_pdl(kernel, grid, block, 0, stream, o, gp, ldg, op, rows, heads, V, eps, gate_kind, weight); };
     if (g_dtype == LLM_F32 && out_dtype == LLM_F32) return go(head_norm_gate_kernel<float, float>, (const float*)g, (float*)out);
     if (g_dtype == LLM_F32 && out_dtype == LLM_BF16) return go(head_norm_gate_kernel<float, bf>, (const float*)g, (bf*)out);
     if (g_dtype == LLM_BF16 && out_dtype == LLM_BF16) return go(head_norm_gate_kernel<bf, bf>, (const bf*)g, (bf*)out);

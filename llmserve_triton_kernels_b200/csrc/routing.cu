@@ -197,6 +197,72 @@ expert_act_scale_kernel(const T* __restrict__ x, int ldx, const float* __restric
     }
 }
 
+// Experts of the gated form whose gate and up products are bounded:
+//     g = min(gate, limit)      u = clamp(up, -limit, limit)      y = g * sigmoid(slope * g) * (u + 1) * weight
+// x [N, ...]: for every expert e its gate columns [e * 2 ff, e * 2 ff + ff) and its up columns behind them, then a shared
+// expert's gate and up columns (fs each, limit_s; fs = 0: none).  y [N, E * ff + fs].  The weight of expert e for token t
+// is w[t, e] (float32, the shared expert's at w[t, E]) or, without w, 1 / top where e is one of the `top` entries of
+// table[ids[t]] and 0 elsewhere (the shared expert 1).  Where the weight is 0 nothing is read.  RUN consecutive columns a
+// thread (16 bytes where sizes and addresses allow, else one).
+template <typename T, int RUN>
+__global__ void __launch_bounds__(256)
+expert_gated_act_kernel(const T* __restrict__ x, int ldx, T* __restrict__ y, int ldy, const float* __restrict__ w, int ldw,
+                        const int* __restrict__ ids, const int* __restrict__ table, int top, int vocab, int E, int ff, int fs,
+                        float limit, float limit_s, float slope) {
+    pdl_trigger();
+    const int t = blockIdx.y;
+    const int C = E * ff + fs;
+    const float share = top > 0 ? 1.f / (float)top : 0.f;
+    const int* mine = nullptr;
+    if (!w) {
+        int id = ids[t];
+        if (id < 0 || id >= vocab) id = 0;
+        mine = table + (size_t)id * top;
+    }
+    pdl_wait();
+    for (int j = (blockIdx.x * blockDim.x + threadIdx.x) * RUN; j < C; j += gridDim.x * blockDim.x * RUN) {
+        const bool shared = j >= E * ff;
+        const int e = shared ? E : j / ff, i = shared ? j - E * ff : j - e * ff;
+        float wt;
+        if (w) wt = w[(size_t)t * ldw + e];
+        else if (shared) wt = 1.f;
+        else {
+            wt = 0.f;
+            for (int c = 0; c < top; ++c) wt = mine[c] == e ? share : wt;
+        }
+        float out[RUN];
+#pragma unroll
+        for (int c = 0; c < RUN; ++c) out[c] = 0.f;
+        if (wt != 0.f) {
+            const int width = shared ? fs : ff;
+            const float lim = shared ? limit_s : limit;
+            const T* gp = x + (size_t)t * ldx + (size_t)E * 2 * ff * (shared ? 1 : 0) + (shared ? 0 : (size_t)e * 2 * ff) + i;
+            float g[RUN], u[RUN];
+            if constexpr (RUN == 4) { load4(gp, g); load4(gp + width, u); }
+            else if constexpr (RUN == 8) {
+                float a[4], b[4];
+                load4(gp, a); load4(gp + 4, b);
+#pragma unroll
+                for (int c = 0; c < 4; ++c) { g[c] = a[c]; g[c + 4] = b[c]; }
+                load4(gp + width, a); load4(gp + width + 4, b);
+#pragma unroll
+                for (int c = 0; c < 4; ++c) { u[c] = a[c]; u[c + 4] = b[c]; }
+            } else { g[0] = to_float(gp[0]); u[0] = to_float(gp[width]); }
+#pragma unroll
+            for (int c = 0; c < RUN; ++c) {
+                const float gc = fminf(g[c], lim), uc = fminf(fmaxf(u[c], -lim), lim);
+                out[c] = gc / (1.f + expf(-slope * gc)) * (uc + 1.f) * wt;
+            }
+        }
+        T* dst = y + (size_t)t * ldy + j;
+        if constexpr (RUN == 4) store4(dst, out);
+        else if constexpr (RUN == 8) {
+            float a[4] = {out[0], out[1], out[2], out[3]}, b[4] = {out[4], out[5], out[6], out[7]};
+            store4(dst, a); store4(dst + 4, b);
+        } else dst[0] = from_float<T>(out[0]);
+    }
+}
+
 // out[t, :] = factor * sum_b  x_b[t, :] / sqrt(mean(x_b[t, :]^2) + eps) * w_b        (b < count <= 4), one CTA per row
 struct Branches {
     const float* x[4];
@@ -352,6 +418,27 @@ LLM_EXPORT int llm_expert_act_scale(const void* x, int ldx, const float* w, int 
         return launch_pdl(expert_act_scale_kernel<float>, grid, block, 0, stream, (const float*)x, ldx, w, ldw, (float*)y, ldy, N, C, E, ff, kind);
     return launch_pdl(expert_act_scale_kernel<__nv_bfloat16>, grid, block, 0, stream, (const __nv_bfloat16*)x, ldx, w, ldw,
                       (__nv_bfloat16*)y, ldy, N, C, E, ff, kind);
+}
+
+LLM_EXPORT int llm_expert_gated_act(const void* x, int ldx, void* y, int ldy, int dtype, const float* w, int ldw, const int* ids,
+                                    const int* table, int top, int vocab, int N, int E, int ff, int fs, float limit, float limit_s,
+                                    float slope, cudaStream_t stream) {
+    const int C = E * ff + fs;
+    if (N <= 0 || C <= 0) return 0;
+    if (E < 0 || ff < 0 || fs < 0 || N > 65535 || (!w && (!ids || !table || top < 0 || vocab <= 0))) return LLM_ERR_BAD_ARGUMENT;
+    const int run = dtype == LLM_F32 ? 4 : 8;
+    const bool wide = ff % run == 0 && fs % run == 0 && ldx % run == 0 && ldy % run == 0 && ((uintptr_t)x | (uintptr_t)y) % 16 == 0;
+    const int per = 256 * (wide ? run : 1), blocks = (C + per - 1) / per;
+    const dim3 grid(blocks < 64 ? blocks : 64, N), block(256);
+    using bf = __nv_bfloat16;
+    auto go = [&](auto kernel, auto* xp, auto* yp) {
+        return launch_pdl(kernel, grid, block, 0, stream, xp, ldx, yp, ldy, w, ldw, ids, table, top, vocab, E, ff, fs, limit, limit_s, slope);
+    };
+    if (dtype == LLM_F32)
+        return wide ? go(expert_gated_act_kernel<float, 4>, (const float*)x, (float*)y) : go(expert_gated_act_kernel<float, 1>, (const float*)x, (float*)y);
+    if (dtype == LLM_BF16)
+        return wide ? go(expert_gated_act_kernel<bf, 8>, (const bf*)x, (bf*)y) : go(expert_gated_act_kernel<bf, 1>, (const bf*)x, (bf*)y);
+    return LLM_ERR_BAD_ARGUMENT;
 }
 
 LLM_EXPORT int llm_branch_norm_sum(const float* x0, const float* w0, const float* x1, const float* w1, const float* x2, const float* w2,

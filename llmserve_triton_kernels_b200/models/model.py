@@ -136,16 +136,30 @@ class Model:
             next_norm = self.blocks[order[i + 1].layer].first_norm() if follows else None
             pending = self.blocks[run.layer].forward(resid, pending, ctx, caches[i], next_norm=next_norm)
             if self.layer_probe is not None:
+                if isinstance(pending, ops.StreamUpdate):
+                    self.layer_probe(i, self._updated_copies(resid, pending).sum(0))
+                    continue
                 delta, alpha = (None, 1.0) if isinstance(pending, ops.NormedInput) else ops.split_pending(pending)
                 self.layer_probe(i, resid if delta is None else resid + alpha * delta.to(resid.dtype))
         if ctx.num_logits == 0:
             return torch.empty((0, self.plan.vocab_size), dtype=torch.float32, device=self.device)
+        if self.plan.streams is not None:
+            # the copies take up the last part's result and are summed, on the wanted rows only, in the final norm's kernel
+            update = pending if isinstance(pending, ops.StreamUpdate) else None
+            return self.project_logits(self.final_norm.add_streams(resid, update, None, rows=ctx.logit_rows))
         delta, alpha = ops.split_pending(pending)
         if alpha != 1.0:
             x = self.final_norm.add_forward(resid, delta, rows=ctx.logit_rows, alpha=alpha)
         else:
             x = self.final_norm.add_forward(resid, delta, rows=ctx.logit_rows)
         return self.project_logits(x)
+
+    @staticmethod
+    def _updated_copies(resid, update):
+        """For looking at the stream only: the copies as they will be once ``update`` has been taken up (a new tensor)."""
+        tensors, factors = update.results()
+        y = sum(f * t.float() for t, f in zip(tensors, factors))
+        return torch.einsum("st,snw->tnw", update.mix.view(resid.shape[0], resid.shape[0]), resid) + update.take.view(-1, 1, 1) * y[None]
 
     def _inject(self, inj, resid, pending, ctx):
         """The stream takes up what the entry in front left, then the token embeddings and/or a vector of the plan."""
@@ -174,6 +188,11 @@ class Model:
         """The residual stream that the first layer meets: the tokens' rows of the table, in 32-bit ``[N, hidden]``.
         An architecture that scales or otherwise prepares its embeddings overrides this in a subclass that it names
         when it registers (``register_architecture(..., model_class=...)``)."""
+        if self.plan.streams is not None:
+            x = ops.embed(ctx.token_ids, self.embedding, copies=self.plan.streams)  # [streams, N, hidden]
+            if self.plan.embedding_scale != 1.0:
+                ops.unary(x.view(-1, x.shape[-1]), "scale", self.plan.embedding_scale, inplace=True)
+            return x
         x = ops.embed(ctx.token_ids, self.embedding)
         if self.plan.embedding_scale != 1.0:
             ops.unary(x, "scale", self.plan.embedding_scale, inplace=True)

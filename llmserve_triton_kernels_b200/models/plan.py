@@ -85,6 +85,7 @@ class ModelPlan:
     extra_tensors: tuple[tuple[str, tuple[int, ...]], ...] = ()  # (name, shape) of tensors that belong to no part
     logit_scale: float = 1.0  # the logits are the output matrix's product times this
     embedding_scale: float = 1.0  # the residual stream starts as the tokens' rows of the table times this
+    streams: int | None = None  # the residual stream is kept in this many copies [streams, N, hidden], all equal at the start (None: one plain stream)
 
     def __post_init__(self) -> None:
         for i, run in enumerate(self.schedule):
@@ -95,6 +96,8 @@ class ModelPlan:
                     raise ValueError(f"schedule entry {i} reads the cache of entry {run.cache_of}, which is not earlier")
                 if self.schedule[run.cache_of].cache_of is not None:
                     raise ValueError(f"schedule entry {i} reads the cache of entry {run.cache_of}, which keeps none itself")
+        if self.streams is not None and (self.streams < 1 or self.injections):
+            raise ValueError("a stream kept in copies needs at least one copy, and takes nothing up between its layers")
         declared = {name for name, _ in self.extra_tensors}
         seen = set()
         for inj in self.injections:

@@ -52,9 +52,9 @@ _SIGNATURES = {
     "llm_merge_two_parts": [_vp, _ll, _ll, _vp, _vp, _ll, _ll, _vp, _vp, _ll, _ll, _i, _i, _i, _vp],
     "llm_unit_norm_kv_write": [_vp, _i, _i, _vp, _vp, _f, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
     "llm_attention_rows": [_vp, _ll, _ll, _i, _vp, _ll, _ll, _i, _vp, _ll, _ll, _vp, _ll, _ll, _ll, _vp, _ll, _ll, _ll, _i, _i,
-                           _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _vp],
+                           _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _vp, _vp, _ll, _vp],
     "llm_attention_rows_mma": [_vp, _ll, _ll, _i, _vp, _ll, _ll, _i, _vp, _ll, _ll, _vp, _ll, _ll, _ll, _vp, _ll, _ll, _ll, _i,
-                               _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _vp, _vp, _i, _vp, _ll, _i, _vp, _vp],
+                               _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _vp, _vp, _i, _vp, _ll, _i, _vp, _vp, _vp, _ll, _vp],
     "llm_gemm_simt_batched": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _ll, _ll, _ll, _vp],
     "llm_sample": [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
     "llm_sigmoid_attention": [_vp, _i, _i, _vp, _i, _vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _f, _i,
@@ -63,7 +63,12 @@ _SIGNATURES = {
     "llm_sigmoid_sum_parts": [_vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _vp],
     "llm_qk_prepare": [_vp, _i, _i, _vp, _i, _i, _vp, _i, _vp, _i, _vp, _i, _i, _vp, _vp, _f, _vp, _i, _vp, _f, _i, _i, _i, _i, _i, _vp],
     "llm_retention_scan": [_vp, _i, _vp, _i, _vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _i, _vp],
-    "llm_head_norm_gate": [_vp, _vp, _i, _i, _vp, _i, _i, _i, _i, _f, _i, _vp],
+    "llm_head_norm_gate": [_vp, _vp, _i, _i, _vp, _i, _i, _i, _i, _f, _i, _vp, _vp],
+    "llm_embed_copies": [_vp, _vp, _i, _vp, _i, _i, _i, _i, _vp],
+    "llm_hyper_mix_norm": [_vp, _vp, _vp, _vp, _vp, _f, _f, _f, _f, _i, _vp, _vp, _vp, _vp, _f, _vp, _vp, _i, _i, _i, _i, _i, _vp],
+    "llm_head_prepare": [_vp, _i, _i, _vp, _vp, _i, _vp, _i, _vp, _i, _i, _vp, _vp, _f, _i, _vp, _i, _vp, _f, _i, _i, _i, _i, _i, _i, _i, _vp],
+    "llm_gated_scan": [_vp, _i, _vp, _i, _vp, _i, _i, _vp, _i, _vp, _f, _f, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
+    "llm_expert_gated_act": [_vp, _i, _vp, _i, _i, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _f, _f, _vp],
     "llm_router": [_vp, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _i, _vp],
     "llm_route_topk": [_vp, _i, _vp, _vp, _i, _i, _i, _f, _i, _i, _vp],
     "llm_expert_act_scale": [_vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
@@ -187,11 +192,16 @@ def _i32(t: torch.Tensor, name: str) -> None:
 
 
 # ------------------------------------------------------------------------------------------------
-def embed(ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
-    """``float32(table[ids])``: ids ``[N]`` int32, table ``[vocab, hidden]`` -> ``[N, hidden]`` float32."""
+def embed(ids: torch.Tensor, table: torch.Tensor, copies: int | None = None) -> torch.Tensor:
+    """``float32(table[ids])``: ids ``[N]`` int32, table ``[vocab, hidden]`` -> ``[N, hidden]`` float32; with ``copies``
+    the rows are written that many times, ``[copies, N, hidden]`` (a residual stream kept in several copies)."""
     _i32(ids, "ids")
     _need(table.dim() == 2 and table.is_contiguous(), "the token table must be a contiguous matrix")
     n, (vocab, hidden) = ids.numel(), table.shape
+    if copies is not None:
+        out = torch.empty((int(copies), n, hidden), dtype=torch.float32, device=table.device)
+        _check(_launch("llm_embed_copies", _ptr(ids), _ptr(table), _code(table.dtype), _ptr(out), n, hidden, vocab, int(copies), _stream()), "embed (copies)")
+        return out
     out = torch.empty((n, hidden), dtype=torch.float32, device=table.device)
     _check(_launch("llm_embed", _ptr(ids), _ptr(table), _code(table.dtype), _ptr(out), n, hidden, vocab, _stream()), "embed")
     return out
@@ -349,9 +359,42 @@ class BranchSum:
         return branch_norm_sum(self.branches, self.weights, self.eps, self.factor)
 
 
+class WeightedSum:
+    """A contribution that is still a list of tensors with a factor each: ``sum_b factors[b] * tensors[b]`` (what mixers
+    side by side return when their outputs meet as a plain weighted sum).  Whoever takes it up in a kernel of its own
+    (:func:`hyper_mix_norm`) reads the tensors; anybody else gets the sum from :meth:`materialize`."""
+
+    def __init__(self, tensors: list[torch.Tensor], factors: list[float]):
+        self.tensors, self.factors = list(tensors), [float(f) for f in factors]
+
+    def materialize(self) -> torch.Tensor:
+        out = unary(self.tensors[0].float() if self.tensors[0].dtype != torch.float32 else self.tensors[0], "scale", self.factors[0])
+        for t, f in zip(self.tensors[1:], self.factors[1:]):
+            out.add_(t.to(out.dtype), alpha=f)
+        return out
+
+
+class StreamUpdate:
+    """What a part between hyper-connections returned, not yet taken up by the copies of the stream: ``result`` (a
+    float32 tensor ``[N, width]`` or a :class:`WeightedSum`), and the part's ``mix [S, S]`` (from, to) and ``take [S]``:
+    ``x_t <- sum_s mix[s, t] x_s + take[t] * result``."""
+
+    def __init__(self, result, mix: torch.Tensor, take: torch.Tensor):
+        self.result, self.mix, self.take = result, mix, take
+
+    def results(self) -> tuple[list[torch.Tensor], list[float]]:
+        if isinstance(self.result, WeightedSum):
+            return self.result.tensors, self.result.factors
+        if isinstance(self.result, Scaled):
+            return [self.result.tensor], [self.result.alpha]
+        if isinstance(self.result, BranchSum):
+            return [self.result.materialize()], [1.0]
+        return [self.result], [1.0]
+
+
 def split_pending(pending) -> tuple[torch.Tensor | None, float]:
     """``(what is still to be added to the stream or None, its factor)`` of what a part or a block returned."""
-    if isinstance(pending, BranchSum):
+    if isinstance(pending, (BranchSum, WeightedSum)):
         return pending.materialize(), 1.0
     if pending is None or pending is ADDED:
         return None, 1.0
@@ -1008,7 +1051,7 @@ def head_linear(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
 def attention_rows(q0, q1, keys, k_strides, values, v_strides, value_dim: int, page_table, page_size: int, ctx, *, num_heads: int,
                    num_kv_heads: int, scale: float, window: int | None = None, slopes: torch.Tensor | None = None,
                    key_part: int = 0, keys1: int | None = None, k1_token: int = 0, fresh_d0: int = 0, want_stats: bool = False,
-                   leave_parts: bool = False):
+                   leave_parts: bool = False, sinks: torch.Tensor | None = None, gate: torch.Tensor | None = None):
     """Attention in its general form: queries ``q0 [N, H, d0]`` and optionally ``q1 [N, H, d1]`` (lanes behind q0's),
     keys and values addressed by ``(page, head, token)`` strides in elements, an optional bias ``-slopes[h] * distance``.
     Returns ``[N, H, value_dim]``.
@@ -1018,8 +1061,16 @@ def attention_rows(q0, q1, keys, k_strides, values, v_strides, value_dim: int, p
     behind them, one row a token for all heads).  With ``want_stats`` the result is ``(out, stats [N, H, 2])``: each row's
     maximum score and sum of exponentials (a row without keys: ``-inf, 0``, and an output that is not to be read), for :func:`merge_two_parts`.
     ``leave_parts``: where the keys are cut over several CTAs the partial results are not merged but returned as an
-    :class:`AttentionParts`, for a kernel that merges them on its way (:func:`merge_project_gate`)."""
+    :class:`AttentionParts`, for a kernel that merges them on its way (:func:`merge_project_gate`).
+    ``sinks`` (float32 ``[H]``): every head's softmax has one more term ``exp(sinks[h])`` in its denominator, with no key and
+    no value.  ``gate`` (float32 ``[N, >= H * value_dim]``, rows may have a pitch): the output is multiplied by its sigmoid."""
     n, d0 = q0.shape[0], q0.shape[2]
+    if sinks is not None:
+        _need(sinks.dtype == torch.float32 and sinks.numel() == num_heads and sinks.is_contiguous(), "sinks must be float32 [heads]")
+    if gate is not None:
+        _need(gate.dtype == torch.float32 and gate.dim() == 2 and gate.stride(1) == 1 and gate.shape[0] == n and gate.shape[1] >= num_heads * value_dim, "the gate must be float32 [N, heads * value_dim]")
+        _need(not leave_parts, "a gate is applied where the output is written, not to partial results")
+    gate_token = 0 if gate is None else gate.stride(0)
     d1 = 0 if q1 is None else q1.shape[2]
     _need(q0.stride(2) == 1 and (q1 is None or q1.stride(2) == 1), "attention_rows: queries need unit inner strides")
     _i32(page_table, "page_table")
@@ -1047,7 +1098,8 @@ def attention_rows(q0, q1, keys, k_strides, values, v_strides, value_dim: int, p
             keys, *k_strides, values, *v_strides,
             value_dim, _ptr(page_table), page_table.shape[1], _ptr(ctx.token_request), _ptr(ctx.cu_tokens), _ptr(ctx.context_lens),
             _ptr(slopes), n, ctx.num_requests, ctx.max_query_len, num_heads, num_kv_heads, page_size, int(window or 0), float(scale),
-            splits, _ptr(part_o), _ptr(part_ml), int(key_part), keys1, int(k1_token), int(fresh_d0), _ptr(stats), _stream(),
+            splits, _ptr(part_o), _ptr(part_ml), int(key_part), keys1, int(k1_token), int(fresh_d0), _ptr(stats), _ptr(sinks), _ptr(gate),
+            gate_token, _stream(),
         )
         if code != 10002:
             _check(code, "attention_rows (tensor cores)")
@@ -1061,7 +1113,8 @@ def attention_rows(q0, q1, keys, k_strides, values, v_strides, value_dim: int, p
         "llm_attention_rows", _ptr(q0), q0.stride(0), q0.stride(1), d0, _ptr(q1), 0 if q1 is None else q1.stride(0),
         0 if q1 is None else q1.stride(1), d1, _ptr(out), out.stride(0), out.stride(1), keys, *k_strides, values, *v_strides,
         value_dim, _code(q0.dtype), _ptr(page_table), page_table.shape[1], _ptr(ctx.token_request), _ptr(ctx.cu_tokens),
-        _ptr(ctx.context_lens), _ptr(slopes), n, num_heads, num_kv_heads, page_size, int(window or 0), float(scale), _stream(),
+        _ptr(ctx.context_lens), _ptr(slopes), n, num_heads, num_kv_heads, page_size, int(window or 0), float(scale), _ptr(sinks),
+        _ptr(gate), gate_token, _stream(),
     )
     _check(code, "attention_rows")
     return out
@@ -1160,6 +1213,161 @@ def biased_paged_attention(qkv: torch.Tensor, pool: torch.Tensor, page_table: to
     out = attention_rows(q, None, _ptr(pool), (page, head, row), values, (page, head, row), value_dim, page_table, page_size, ctx,
                          num_heads=num_heads, num_kv_heads=num_kv_heads, scale=scale, window=window, slopes=slopes)
     return out.view(qkv.shape[0], num_heads * value_dim)
+
+
+def paged_softmax_attention(q: torch.Tensor, pool: torch.Tensor, page_table: torch.Tensor, ctx, *, num_heads: int, num_kv_heads: int,
+                            key_dim: int, value_dim: int, scale: float, window: int | None = None, sinks: torch.Tensor | None = None,
+                            gate: torch.Tensor | None = None) -> torch.Tensor:
+    """Grouped-query softmax attention of prepared queries ``q [N, num_heads * key_dim]`` over keys and values in
+    ``pool [pages, 2, kv_heads, page_size, D]`` (``D >= key_dim, value_dim``), with an optional sink per head and an
+    optional sigmoid gate on the output (see :func:`attention_rows`).  Returns ``[N, num_heads * value_dim]``."""
+    _need(q.dim() == 2 and q.stride(1) == 1 and q.shape[1] == num_heads * key_dim, "paged_softmax_attention: q [N, heads * key_dim]")
+    _need(pool.dtype == q.dtype and pool.is_contiguous() and pool.dim() == 5 and tuple(pool.shape[1:3]) == (2, num_kv_heads), "the pool plane does not match the heads")
+    page_size, row = pool.shape[3], pool.shape[4]
+    _need(row >= max(key_dim, value_dim), "the pool's rows are shorter than a key or a value")
+    q3 = q.as_strided((q.shape[0], num_heads, key_dim), (q.stride(0), key_dim, 1), q.storage_offset())
+    head, page = page_size * row, 2 * num_kv_heads * page_size * row
+    values = pool.data_ptr() + num_kv_heads * head * pool.element_size()
+    out = attention_rows(q3, None, _ptr(pool), (page, head, row), values, (page, head, row), value_dim, page_table, page_size, ctx,
+                         num_heads=num_heads, num_kv_heads=num_kv_heads, scale=scale, window=window, sinks=sinks, gate=gate)
+    return out.view(q.shape[0], num_heads * value_dim)
+
+
+def head_prepare(proj: torch.Tensor, positions: torch.Tensor | None, *, heads: int, kv_heads: int, dim: int, value_dim: int = 0,
+                 bias: torch.Tensor | None = None, q_weight: torch.Tensor | None = None, k_weight: torch.Tensor | None = None,
+                 eps: float = 0.0, freq: torch.Tensor | None = None, warm: tuple[float, int] | None = None,
+                 values_are_keys: bool = False, pool: torch.Tensor | None = None, slot_map: torch.Tensor | None = None,
+                 out_dtype: torch.dtype | None = None) -> torch.Tensor:
+    """From a token's stacked projections ``proj`` rows ``[heads x dim | kv_heads x dim | kv_heads x value_dim]`` to
+    queries, keys and values, in this order: ``bias`` (float32, laid out like the row) is added; with ``q_weight`` /
+    ``k_weight`` (float32 ``[dim]``) every head is RMS-normed over its lanes (``eps`` inside the root) and weighted; with
+    ``freq`` (float32 ``[rot / 2]``) lanes ``i`` and ``i + rot/2`` of every head turn by ``position * freq[i]``; with
+    ``warm = (coef, every)`` queries are multiplied by ``1 + coef * ln(floor((position + 1) / every) + 1)``.  Keys and values
+    go to the tokens' slots of ``pool [pages, 2, kv_heads, page_size, D]``; with ``values_are_keys`` there are no value
+    columns and a key head's value is that head with its bias, before norm and rotation.  ``kv_heads = 0``: queries only.
+    Returns the queries ``[N, heads * dim]`` in ``out_dtype`` (default: the pool's type)."""
+    cols = (heads + kv_heads) * dim + (0 if values_are_keys else kv_heads * value_dim)
+    _need(proj.dim() == 2 and proj.stride(1) == 1 and proj.shape[1] >= cols, "head_prepare: proj rows are too short")
+    n = proj.shape[0]
+    rot = 0
+    if freq is not None:
+        _need(freq.dtype == torch.float32 and freq.is_contiguous(), "head_prepare: freq is float32")
+        rot = 2 * freq.numel()
+    if rot or warm:
+        _i32(positions, "positions")
+    if bias is not None:
+        _need(bias.dtype == torch.float32 and bias.is_contiguous() and bias.numel() == cols, "head_prepare: the bias is float32, laid out like the row")
+    normed = q_weight is not None
+    for w in (q_weight, k_weight):
+        _need(w is None or (w.dtype == torch.float32 and w.is_contiguous() and w.numel() == dim), "head_prepare: norm weights are float32 [dim]")
+    if kv_heads:
+        _need(pool is not None and pool.is_contiguous() and pool.dim() == 5 and tuple(pool.shape[1:3]) == (2, kv_heads), "the pool plane does not match the heads")
+        _need(not normed or k_weight is not None, "head_prepare: normed keys need a weight")
+        _i32(slot_map, "slot_map")
+        out_dtype = pool.dtype
+    out_dtype = out_dtype or proj.dtype
+    q = torch.empty((n, heads * dim), dtype=out_dtype, device=proj.device)
+    coef, every = (float(warm[0]), int(warm[1])) if warm else (0.0, 0)
+    code = _launch(
+        "llm_head_prepare", _ptr(proj), _code(proj.dtype), proj.stride(0), _ptr(bias), _ptr(q), q.stride(0), _ptr(pool) if kv_heads else None,
+        _code(out_dtype), _ptr(slot_map) if kv_heads else None, pool.shape[3] if kv_heads else 1, pool.shape[4] if kv_heads else dim,
+        _ptr(q_weight), _ptr(k_weight), float(eps), int(normed), _ptr(freq), rot, _ptr(positions) if (rot or warm) else None, coef, every,
+        n, heads, kv_heads, dim, value_dim, int(values_are_keys), _stream(),
+    )
+    _check(code, "head_prepare")
+    return q
+
+
+def hyper_mix_norm(streams: torch.Tensor, update: "StreamUpdate | None", read_in: torch.Tensor | None, weight: torch.Tensor, eps: float,
+                   rows: torch.Tensor | None = None, out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    """One pass over the copies ``streams [S, N, W]`` (float32) of a residual stream between two parts: with ``update`` the
+    copies take up what the part in front returned, ``x_t <- sum_s mix[s, t] x_s + take[t] * result`` (in place); then
+    ``u = sum_t read_in[t] x_t`` (``read_in`` None: the plain sum) and the result is ``u * rsqrt(mean(u^2) + eps) * weight``
+    in ``out_dtype``.  With ``rows`` (int32) only those rows are produced and the copies are left as they were."""
+    _need(streams.dtype == torch.float32 and streams.dim() == 3 and streams.is_contiguous(), "hyper_mix_norm: the copies are contiguous float32 [S, N, W]")
+    S, n, w = streams.shape
+    _need(weight.dtype == torch.float32 and weight.is_contiguous() and weight.numel() == w, "hyper_mix_norm: the norm weight is float32 [W]")
+    ys, fs = ([], [])
+    if update is not None:
+        ys, fs = update.results()
+        _need(1 <= len(ys) <= 4, "hyper_mix_norm: a part's result is a weighted sum of one to four tensors")
+        for y in ys:
+            _need(y.dtype == torch.float32 and y.is_contiguous() and tuple(y.shape) == (n, w), "hyper_mix_norm: results are contiguous float32 [N, W]")
+        for t, size in ((update.mix, S * S), (update.take, S)):
+            _need(t.dtype == torch.float32 and t.is_contiguous() and t.numel() == size, "hyper_mix_norm: mix [S, S] and take [S] are float32")
+    if read_in is not None:
+        _need(read_in.dtype == torch.float32 and read_in.is_contiguous() and read_in.numel() == S, "hyper_mix_norm: read_in is float32 [S]")
+    if rows is not None:
+        _i32(rows, "rows")
+    n_out = n if rows is None else rows.numel()
+    out = torch.empty((n_out, w), dtype=out_dtype, device=streams.device)
+    yp = [_ptr(ys[i]) if i < len(ys) else None for i in range(4)]
+    fp = [float(fs[i]) if i < len(fs) else 0.0 for i in range(4)]
+    code = _launch("llm_hyper_mix_norm", _ptr(streams), *yp, *fp, len(ys), _ptr(update.mix) if update is not None else None,
+                   _ptr(update.take) if update is not None else None, _ptr(read_in), _ptr(weight), float(eps), _ptr(rows), _ptr(out),
+                   _code(out_dtype), n_out, S, n, w, _stream())
+    _check(code, "hyper_mix_norm")
+    return out
+
+
+def linear32(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """``x [M, K] @ w [N, K]^T`` for an input that stays 32-bit whatever the weights' type: true 32-bit multiply-adds on
+    the CUDA cores, float32 out (a small product on the way into a recurrence)."""
+    _need(x.dim() == 2 and w.dim() == 2 and x.shape[1] == w.shape[1] and x.dtype == torch.float32, f"linear32: shapes {tuple(x.shape)} and {tuple(w.shape)} do not match, or x is not float32")
+    _need(x.stride(1) == 1 and w.is_contiguous(), "linear32: operands must have unit inner stride")
+    m, k = x.shape
+    n = w.shape[0]
+    out = torch.empty((m, n), dtype=torch.float32, device=x.device)
+    code = _launch("llm_gemm_simt", _ptr(x), _F32, _ptr(w), _code(w.dtype), _ptr(out), _F32, m, n, k, x.stride(0), k, n, _stream())
+    _check(code, "linear32")
+    return out
+
+
+def gated_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, z: torch.Tensor, z_bias: torch.Tensor | None, inv_tau: float,
+               q_scale: float, states: torch.Tensor, state_slots: torch.Tensor, cu_tokens: torch.Tensor, num_requests: int, heads: int,
+               dim: int, value_dim: int, max_query_len: int = 0) -> torch.Tensor:
+    """``S = diag(alpha_t) S + k_t v_t^T``, ``o_t = S^T (q_scale * q_t)`` per head over every request's new tokens, with a
+    decay per key channel that the token chooses: ``alpha_t = sigmoid(z_t + z_bias) ^ inv_tau``.  From and to
+    ``states[state_slots[r]]`` (``[slots, heads, dim, value_dim]`` float32).  ``q, k, z [N, heads * dim]`` float32 and
+    ``v [N, heads * value_dim]`` (views with a row pitch will do).  Returns ``o [N, heads, value_dim]`` float32."""
+    for t in (q, k, z):
+        _need(t.dtype == torch.float32 and t.stride(1) == 1 and t.shape[1] == heads * dim, "gated_scan: q, k and the decays' logits are float32 [N, heads * dim]")
+    _need(v.stride(1) == 1 and v.shape[1] == heads * value_dim, "gated_scan: v [N, heads * value_dim]")
+    _need(states.dtype == torch.float32 and states.is_contiguous() and tuple(states.shape[1:]) == (heads, dim, value_dim), "gated_scan: states [slots, heads, dim, value_dim] float32")
+    _need(z_bias is None or (z_bias.dtype == torch.float32 and z_bias.is_contiguous() and z_bias.numel() == heads * dim), "gated_scan: the bias is float32 [heads * dim]")
+    _i32(state_slots, "state_slots")
+    _i32(cu_tokens, "cu_tokens")
+    out = torch.empty((q.shape[0], heads, value_dim), dtype=torch.float32, device=q.device)
+    few = 0 < int(max_query_len) <= 16
+    code = _launch("llm_gated_scan", _ptr(q), q.stride(0), _ptr(k), k.stride(0), _ptr(v), _code(v.dtype), v.stride(0), _ptr(z), z.stride(0),
+                   _ptr(z_bias), float(inv_tau), float(q_scale), _ptr(states), _ptr(state_slots), _ptr(cu_tokens), _ptr(out), int(num_requests),
+                   heads, dim, value_dim, int(few), _stream())
+    _check(code, "gated_scan")
+    return out
+
+
+def expert_gated_act(x: torch.Tensor, experts: int, ff: int, shared_ff: int, limit: float, shared_limit: float, slope: float, *,
+                     weights: torch.Tensor | None = None, ids: torch.Tensor | None = None, table: torch.Tensor | None = None) -> torch.Tensor:
+    """The activation of gated experts whose products are bounded, times each token's weight of the expert:
+    ``g = min(gate, limit)``, ``u = clamp(up, -limit, limit)``, ``y = g * sigmoid(slope * g) * (u + 1) * weight``.
+    ``x [N, experts * 2 ff + 2 shared_ff]``: per expert its gate columns, then its up columns; a shared expert's behind them
+    (``shared_limit``).  The weight is ``weights[t, e]`` (float32 ``[N, experts (+ 1)]``) or, from ``ids [N]`` and
+    ``table [vocab, top]`` (int32), ``1 / top`` for the experts that the table lists for the token's id, 0 for the others and
+    1 for the shared one.  Returns ``[N, experts * ff + shared_ff]``."""
+    _need(x.dim() == 2 and x.stride(1) == 1 and x.shape[1] >= 2 * (experts * ff + shared_ff), "expert_gated_act: x rows hold every expert's gate and up columns")
+    top = vocab = ldw = 0
+    if weights is not None:
+        _need(weights.dtype == torch.float32 and weights.stride(1) == 1 and weights.shape[0] == x.shape[0] and weights.shape[1] >= experts + int(shared_ff > 0), "expert_gated_act: weights are float32 [N, experts (+ 1)]")
+        ldw = weights.stride(0)
+    else:
+        _i32(ids, "ids")
+        _need(table is not None and table.dtype == torch.int32 and table.is_contiguous() and table.dim() == 2 and ids.numel() == x.shape[0], "expert_gated_act: table is int32 [vocab, top]")
+        vocab, top = table.shape
+    out = torch.empty((x.shape[0], experts * ff + shared_ff), dtype=x.dtype, device=x.device)
+    code = _launch("llm_expert_gated_act", _ptr(x), x.stride(0), _ptr(out), out.stride(0), _code(x.dtype), _ptr(weights), ldw, _ptr(ids),
+                   _ptr(table), top, vocab, x.shape[0], experts, ff, shared_ff, float(limit), float(shared_limit), float(slope), _stream())
+    _check(code, "expert_gated_act")
+    return out
 
 
 # ------------------------------------------------------------------------------------------------
@@ -1294,9 +1502,11 @@ def retention_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: tor
 
 
 def head_norm_gate(o: torch.Tensor, gate: torch.Tensor | None, eps: float | None, kind: str = "silu",
-                   out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+                   out_dtype: torch.dtype = torch.float32, weight: torch.Tensor | None = None) -> torch.Tensor:
     """``o [N, heads, W]`` (float32): every head divided by its root mean square ``sqrt(mean(o^2) + eps)`` (``eps`` None:
-    not), times ``kind`` (``silu`` or ``sigmoid``) of ``gate [N, heads * W]`` (None: no gate) -> ``[N, heads * W]``."""
+    not) and multiplied by ``weight`` (float32 ``[W]``, the same for every head; None: not), times ``kind`` (``silu`` or
+    ``sigmoid``) of ``gate [N, heads * W]`` (None: no gate) -> ``[N, heads * W]``."""
+    _need(weight is None or (weight.dtype == torch.float32 and weight.is_contiguous() and weight.numel() == o.shape[2]), "head_norm_gate: the weight is float32 [W]")
     _need(o.dtype == torch.float32 and o.is_contiguous() and o.dim() == 3, "head_norm_gate: o is contiguous float32 [N, heads, W]")
     n, heads, w = o.shape
     if gate is not None:
@@ -1304,7 +1514,7 @@ def head_norm_gate(o: torch.Tensor, gate: torch.Tensor | None, eps: float | None
     out = torch.empty((n, heads * w), dtype=out_dtype, device=o.device)
     code = _launch("llm_head_norm_gate", _ptr(o), _ptr(gate), _code(gate.dtype) if gate is not None else _code(out_dtype),
                    0 if gate is None else gate.stride(0), _ptr(out), _code(out_dtype), n, heads, w,
-                   -1.0 if eps is None else float(eps), _GATE_KINDS[kind] if gate is not None else -1, _stream())
+                   -1.0 if eps is None else float(eps), _GATE_KINDS[kind] if gate is not None else -1, _ptr(weight), _stream())
     _check(code, "head_norm_gate")
     return out
 

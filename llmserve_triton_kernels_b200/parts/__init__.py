@@ -16,4 +16,4 @@ from .base import (  # noqa: F401
     build_part,
     register_part,
 )
-from . import attention, block, feed_forward, latent_attention, norm, parallel, recurrent, rotary, sigmoid_attention  # noqa: F401,E402
+from . import attention, block, feed_forward, latent_attention, norm, parallel, recurrent, rotary, sigmoid_attention, softmax_attention  # noqa: F401,E402

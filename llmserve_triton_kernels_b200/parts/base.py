@@ -33,9 +33,10 @@ import torch
 class TensorSpec:
     """One tensor a part owns: its shape and how a random model fills it."""
 
-    shape: tuple[int, ...]
-    init: str = "normal"  # "normal": N(0, std); "ones_plus_normal": 1 + N(0, std); "zeros"
+    shape: tuple[int, ...]  # an extent of -1: any size, known only from the checkpoint (a random model takes ``free_size``)
+    init: str = "normal"  # "normal": N(0, std); "ones_plus_normal": 1 + N(0, std); "zeros"; "distinct:<count>": int32 rows of different ids
     optional: bool = False  # absent from a checkpoint without error (e.g. a tied head)
+    free_size: int = 16  # what a random model uses for an extent of -1
 
 
 @dataclass(frozen=True)

@@ -104,5 +104,75 @@ class MixerOnlyBlock(PreNormBlock):
         return self._scaled(self.mixer.forward(x, ctx, cache, sink=sink) if sink else self.mixer.forward(x, ctx, cache))
 
 
+class HyperConnectionBlock(Block):
+    """A pre-norm layer over a residual stream kept in S copies ``x_1 .. x_S`` (hyper-connections).  For each of its parts
+    q (1: the mixer, 2: the feed-forward) it owns ``hc<q>.in [S]``, ``hc<q>.out [S]`` and ``hc<q>.mix [S, S]``:
+
+        u = sum_s in[s] x_s        y = part(norm(u))        x_t <- sum_s mix[s, t] x_s + out[t] * y     (all t at once)
+
+    ``resid`` is ``[S, N, hidden]`` (``ModelPlan.streams``).  What a part returns travels as an ``ops.StreamUpdate``; the
+    copies take it up in the same kernel that reads them in and norms for the next part (``Norm.add_streams``), so a
+    part costs one pass over the copies.  ``feed_forward`` may be absent (None): the layer then has no second part."""
+
+    roles = {"mixer_norm": "norm", "mixer": "mixer", "ff_norm": "norm", "feed_forward": "feed_forward"}
+
+    def __init__(self, mixer_norm: Norm, mixer: Mixer, ff_norm: Norm | None = None, feed_forward: FeedForward | None = None,
+                 streams: int = 1, names: tuple[str, str] = ("hc1", "hc2")):
+        if not 1 <= int(streams) <= 8:
+            raise ValueError(f"a residual stream is kept in one to eight copies, got {streams}")
+        self.mixer_norm, self.mixer, self.ff_norm, self.feed_forward = mixer_norm, mixer, ff_norm, feed_forward
+        self.streams, self.names = int(streams), tuple(names)
+        self.hc: list[tuple[torch.Tensor, torch.Tensor, torch.Tensor]] = []  # per part: (in, mix, out), 32-bit
+
+    def owned_parts(self):
+        return [p for p in (self.mixer_norm, self.mixer, self.ff_norm, self.feed_forward) if p is not None]
+
+    @property
+    def graph_safe(self) -> bool:
+        return all(p.graph_safe for p in self.owned_parts())
+
+    def _parts(self) -> int:
+        return 1 if self.feed_forward is None else 2
+
+    def tensors(self):
+        from .base import TensorSpec
+
+        S, specs = self.streams, {}
+        for name in self.names[: self._parts()]:
+            specs[f"{name}.in"] = TensorSpec((S,), init="ones_plus_normal")
+            specs[f"{name}.out"] = TensorSpec((S,), init="ones_plus_normal")
+            specs[f"{name}.mix"] = TensorSpec((S, S), init="eye_plus_normal")
+        return specs
+
+    def bind(self, tensors, dtype, device) -> None:
+        f32 = lambda t: t.to(device=device, dtype=torch.float32).contiguous()  # noqa: E731
+        self.hc = [(f32(tensors[f"{n}.in"]), f32(tensors[f"{n}.mix"]), f32(tensors[f"{n}.out"])) for n in self.names[: self._parts()]]
+
+    def forward(self, resid, pending, ctx, cache, next_norm=None):
+        if resid.dim() != 3 or resid.shape[0] != self.streams:
+            raise RuntimeError(f"this block reads a residual stream in {self.streams} copies, got a tensor of shape {tuple(resid.shape)}")
+        if pending is not None and not isinstance(pending, ops.StreamUpdate):
+            raise RuntimeError("a stream kept in copies takes up what a part returned together with that part's mixing weights")
+        read_in, mix, take = self.hc[0]
+        x = self.mixer_norm.add_streams(resid, pending, read_in)
+        pending = ops.StreamUpdate(self.mixer.forward(x, ctx, cache), mix, take)
+        if self.feed_forward is None:
+            return pending
+        read_in, mix, take = self.hc[1]
+        x = self.ff_norm.add_streams(resid, pending, read_in)
+        return ops.StreamUpdate(self.feed_forward.forward(x, ctx), mix, take)
+
+
+class HyperConnectionMixerOnlyBlock(HyperConnectionBlock):
+    """The same without a feed-forward: one part a layer."""
+
+    roles = {"mixer_norm": "norm", "mixer": "mixer"}
+
+    def __init__(self, mixer_norm: Norm, mixer: Mixer, streams: int = 1, names: tuple[str, str] = ("hc1", "hc2")):
+        super().__init__(mixer_norm, mixer, None, None, streams=streams, names=names)
+
+
+register_part("block", "hyper_connection", HyperConnectionBlock)
+register_part("block", "hyper_connection_mixer_only", HyperConnectionMixerOnlyBlock)
 register_part("block", "pre_norm", PreNormBlock)
 register_part("block", "pre_norm_mixer_only", MixerOnlyBlock)

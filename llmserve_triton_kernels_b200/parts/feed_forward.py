@@ -183,3 +183,67 @@ class RoutedMLP(FeedForward):
 
 
 register_part("feed_forward", "routed_mlp", RoutedMLP)
+
+
+class TableRoutedMLP(FeedForward):
+    """A mixture of small gated feed-forward layers without a router: a table gives every token id its ``top`` experts
+    (the entries of a row differ), each with weight ``1 / top``; a shared expert of the same form may run for every token.
+
+        expert(x):  g = min(W_gate x, limit)     u = clamp(W_up x, -limit, limit)
+                    W_down (g * sigmoid(slope * g) * (u + 1))
+        out = (1 / top) * sum over table[token id] of expert_e(x)  +  shared(x)
+
+    Tensors: ``table [vocab, top]`` (integers), ``e<i>.gate``, ``e<i>.up``, ``e<i>.down``, ``shared.gate``, ``shared.up``,
+    ``shared.down``.  As in :class:`RoutedMLP` all experts' gate and up matrices are stacked (the shared expert's last)
+    and so are the down matrices side by side: a step is one product over every expert, one kernel that applies the
+    bounds, the activation and the token's weight of each expert's block of columns (0 for an expert the table does not
+    give the token, whose columns are then not even read), and one product that sums over the experts by itself."""
+
+    graph_safe = True
+    accepts_sink = True
+
+    def __init__(self, hidden_size: int, vocab_size: int, experts: int, top: int, expert_size: int, limit: float,
+                 shared_size: int | None = None, shared_limit: float | None = None, slope: float = 1.702):
+        if not 1 <= int(top) <= int(experts):
+            raise ValueError(f"a token uses {top} of {experts} experts")
+        self.hidden_size, self.vocab_size, self.experts, self.top = int(hidden_size), int(vocab_size), int(experts), int(top)
+        self.expert_size, self.limit, self.slope = int(expert_size), float(limit), float(slope)
+        self.shared_size = int(shared_size) if shared_size else 0
+        self.shared_limit = float(shared_limit) if shared_limit is not None else self.limit
+        self.table = self.w_up = self.w_down = None
+
+    def tensors(self) -> dict[str, TensorSpec]:
+        h, f = self.hidden_size, self.expert_size
+        specs = {"table": TensorSpec((self.vocab_size, self.top), init=f"distinct:{self.experts}")}
+        for e in range(self.experts):
+            specs[f"e{e}.gate"] = TensorSpec((f, h))
+            specs[f"e{e}.up"] = TensorSpec((f, h))
+            specs[f"e{e}.down"] = TensorSpec((h, f))
+        if self.shared_size:
+            specs["shared.gate"] = TensorSpec((self.shared_size, h))
+            specs["shared.up"] = TensorSpec((self.shared_size, h))
+            specs["shared.down"] = TensorSpec((h, self.shared_size))
+        return specs
+
+    def bind(self, tensors, dtype, device) -> None:
+        names = [f"e{e}." for e in range(self.experts)] + (["shared."] if self.shared_size else [])
+        ups = [tensors[p + k] for p in names for k in ("gate", "up")]
+        self.w_up = torch.cat([t.to(dtype) for t in ups], dim=0).to(device).contiguous()  # [E 2 ff + 2 shared, hidden]
+        self.w_down = torch.cat([tensors[p + "down"].to(dtype) for p in names], dim=1).to(device).contiguous()  # [hidden, E ff + shared]
+        table = tensors["table"]
+        if table.is_floating_point() or int(table.min()) < 0 or int(table.max()) >= self.experts:
+            raise ValueError("the experts' table must hold integers below the number of experts")
+        self.table = table.to(device=device, dtype=torch.int32).contiguous()
+
+    def forward(self, x, ctx, sink=None):
+        xt = x.materialize() if isinstance(x, ops.NormedInput) else x
+        act = ops.expert_gated_act(ops.linear(xt, self.w_up), self.experts, self.expert_size, self.shared_size, self.limit,
+                                   self.shared_limit, self.slope, ids=ctx.token_ids, table=self.table)
+        if sink is not None:
+            handed_on = sink.linear(act, self.w_down)
+            if handed_on is not None:
+                return handed_on
+        return ops.linear(act, self.w_down, out_dtype=torch.float32)
+
+
+register_part("feed_forward", "table_routed_mlp", TableRoutedMLP)

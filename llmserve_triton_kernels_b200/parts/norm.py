@@ -53,6 +53,14 @@ class RMSNorm(Norm):
             return None
         return ops.branch_sum_rmsnorm(pending, resid, self.weight, self.eps, self.out_dtype)
 
+    def add_streams(self, streams, update, read_in, rows=None):
+        """For a residual stream kept in several copies (``streams [S, N, size]``): the copies take up ``update`` (an
+        ``ops.StreamUpdate`` or None) in place, are read in with the weights ``read_in [S]`` (None: summed) and the result
+        is normed, all in one kernel.  With ``rows`` only those rows are produced and the copies stay as they were."""
+        if self.groups != 1:
+            raise NotImplementedError("a norm in groups behind a stream kept in copies is not built")
+        return ops.hyper_mix_norm(streams, update, read_in, self.weight, self.eps, rows=rows, out_dtype=self.out_dtype)
+
     def add_forward(self, resid, delta, rows=None, alpha: float = 1.0):
         if self.groups == 1 and alpha == 1.0:
             return ops.rmsnorm(resid, self.weight, self.eps, delta=delta, rows=rows, out_dtype=self.out_dtype)

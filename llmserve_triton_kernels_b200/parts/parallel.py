@@ -2,7 +2,8 @@
 
     factor * sum_b  rmsnorm(branch_b(x)) * w_b            (factor = 1 / branches: the mean)
 
-each output RMS-normed over the model width by itself (``eps`` inside the root) with a weight of its own.  A branch is
+each output RMS-normed over the model width by itself (``eps`` inside the root) with a weight of its own; or, with
+``branch_norm=False``, as the plain weighted sum ``sum_b scales[b] * branch_b(x)`` without norms and weights.  A branch is
 any registered mixer; what it keeps per request (pages, a state slot) is its own: the cache manager holds every
 branch's as a part of a ``CompositeSpec``.  The branches' products leave their results in 32-bit, the norms and the
 sum are 32-bit, and the result is a contribution to the residual stream.
@@ -23,12 +24,17 @@ from .base import CompositeSpec, Mixer, PartSpec, TensorSpec, build_part, regist
 
 class ParallelMixer(Mixer):
     def __init__(self, hidden_size: int, branches: dict[str, PartSpec], norm_eps: float, factor: float | None = None,
-                 weight_name: str = "out"):
+                 weight_name: str = "out", branch_norm: bool = True, scales: list[float] | None = None):
         """``branches``: name -> the mixer's spec; the name, with a dot, is the prefix of the branch's tensors, and
-        ``<name>.<weight_name>`` the weight of its output norm."""
+        ``<name>.<weight_name>`` the weight of its output norm.  ``branch_norm=False``: the outputs are not normed and
+        have no weights; branch b enters the sum times ``scales[b]`` (default 1)."""
         if not 1 <= len(branches) <= 4:
             raise ValueError(f"one to four branches run side by side, got {len(branches)}")
         self.hidden_size, self.norm_eps, self.weight_name = int(hidden_size), float(norm_eps), weight_name
+        self.branch_norm = bool(branch_norm)
+        self.scales = [1.0] * len(branches) if scales is None else [float(v) for v in scales]
+        if len(self.scales) != len(branches) or (self.branch_norm and scales is not None):
+            raise ValueError("scales: one for each branch, for branches that meet as a plain weighted sum")
         self.factor = 1.0 / len(branches) if factor is None else float(factor)
         self.branch_names = tuple(branches)
         for name, spec in branches.items():
@@ -52,14 +58,16 @@ class ParallelMixer(Mixer):
         for name, branch in zip(self.branch_names, self.branches):
             for local, spec in branch.tensors().items():
                 specs[f"{name}.{local}"] = spec
-            specs[f"{name}.{self.weight_name}"] = TensorSpec((self.hidden_size,), init="ones_plus_normal")
+            if self.branch_norm:
+                specs[f"{name}.{self.weight_name}"] = TensorSpec((self.hidden_size,), init="ones_plus_normal")
         return specs
 
     def bind(self, tensors, dtype, device) -> None:
         self.out_weights = []
         for name, branch in zip(self.branch_names, self.branches):
             branch.bind({local: tensors[f"{name}.{local}"] for local in branch.tensors()}, dtype, device)
-            self.out_weights.append(tensors[f"{name}.{self.weight_name}"].to(device=device, dtype=torch.float32).contiguous())
+            if self.branch_norm:
+                self.out_weights.append(tensors[f"{name}.{self.weight_name}"].to(device=device, dtype=torch.float32).contiguous())
         if len(self.branches) > 1 and all(getattr(b, "takes_projection", False) and getattr(b, "w_in", None) is not None for b in self.branches):
             self.w_in = torch.cat([b.w_in for b in self.branches], dim=0).contiguous()
             start = 0
@@ -82,6 +90,8 @@ class ParallelMixer(Mixer):
             else:
                 out = branch.forward(x, ctx, view)
             outs.append(out if out.dtype == torch.float32 else out.float())
+        if not self.branch_norm:  # still a list: whoever takes the sum up may read the branches in a kernel of its own
+            return ops.WeightedSum(outs, self.scales)
         # still a list of branches: the norm behind this mixer may do the meeting, the sum into the stream and itself in one kernel
         return ops.BranchSum(outs, self.out_weights, self.norm_eps, self.factor)
 

@@ -69,6 +69,11 @@ def read_safetensors(model_dir: str | Path) -> dict[str, torch.Tensor]:
     return tensors
 
 
+def _fits(got: tuple, declared: tuple) -> bool:
+    """A declared extent of -1 takes any size (a size that only the checkpoint knows)."""
+    return len(got) == len(declared) and all(d == -1 or d == g for g, d in zip(got, declared))
+
+
 def check_tensors(
     tensors: dict[str, torch.Tensor],
     specs: dict[str, TensorSpec],
@@ -80,7 +85,7 @@ def check_tensors(
     wrong = [
         (n, tuple(s.shape), tuple(tensors[n].shape))
         for n, s in specs.items()
-        if n in tensors and tuple(tensors[n].shape) != tuple(s.shape)
+        if n in tensors and not _fits(tuple(tensors[n].shape), tuple(s.shape))
     ]
     if missing or unexpected or wrong:
         raise WeightError(missing, unexpected, wrong, where)

@@ -4,7 +4,7 @@ The reference's ``random_model`` (src/llmserve/weights.py:60-79) draws from one 
 module order.  Here every tensor has a generator of its own, seeded from the seed and the
 tensor's name, so the values do not depend on the order or on how a part stacks its matrices.
 Matrices are N(0, std); norm weights are 1 + N(0, std), so that a norm that forgot its weight
-shows in the logits.
+shows in the logits; integer tables (``distinct:<count>``) hold different ids below the count in every row.
 """
 
 from __future__ import annotations
@@ -23,11 +23,20 @@ def _generator(seed: int, name: str) -> torch.Generator:
 
 
 def random_tensor(name: str, spec: TensorSpec, seed: int, std: float, dtype: torch.dtype) -> torch.Tensor:
+    if any(d == -1 for d in spec.shape):  # a size that only a checkpoint knows: a random model takes the spec's stand-in
+        spec = TensorSpec(tuple(spec.free_size if d == -1 else d for d in spec.shape), spec.init, spec.optional, spec.free_size)
     if spec.init == "zeros":
         return torch.zeros(spec.shape, dtype=dtype)
+    if spec.init.startswith("distinct:"):  # an integer table whose rows hold different ids below a count
+        count = int(spec.init.split(":")[1])
+        rows, per_row = spec.shape
+        order = torch.rand((rows, count), generator=_generator(seed, name)).argsort(dim=1)
+        return order[:, :per_row].to(torch.int32).contiguous()
     values = torch.randn(spec.shape, generator=_generator(seed, name), dtype=torch.float32) * std
     if spec.init == "ones_plus_normal":
         values = values + 1.0
+    elif spec.init == "eye_plus_normal":
+        values = values + torch.eye(spec.shape[0], spec.shape[1])
     elif spec.init != "normal":
         raise ValueError(f"tensor {name!r} has an unknown init {spec.init!r}")
     return values.to(dtype)

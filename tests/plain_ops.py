@@ -12,8 +12,9 @@ import torch
 import plain_llama
 
 
-def embed(ids, table):
-    return table[ids.long()].float()
+def embed(ids, table, copies=None):
+    rows = table[ids.long()].float()
+    return rows if copies is None else rows[None].repeat(int(copies), 1, 1)
 
 
 def rmsnorm(resid, weight, eps, delta=None, rows=None, out_dtype=torch.float32):
@@ -247,8 +248,9 @@ def head_linear(x, w):
     return torch.einsum("nhk,hmk->nhm", x.float(), w.float()).to(x.dtype)
 
 
-def _attend(q, k, v, first_pos, scale, window, slopes):
-    """q [T, H, dk], k [n, H, dk], v [n, H, dv] float32; query t stands at position first_pos + t."""
+def _attend(q, k, v, first_pos, scale, window, slopes, sinks=None):
+    """q [T, H, dk], k [n, H, dk], v [n, H, dv] float32; query t stands at position first_pos + t.  ``sinks [H]``: a score
+    per head that stands in every row's softmax without a value."""
     n = k.shape[0]
     s = torch.einsum("thd,jhd->htj", q, k) * scale
     pos = torch.arange(first_pos, first_pos + q.shape[0], device=q.device)[:, None]
@@ -259,6 +261,9 @@ def _attend(q, k, v, first_pos, scale, window, slopes):
     if window:
         visible = visible & (j > pos - window)
     s = s.masked_fill(~visible[None], float("-inf"))
+    if sinks is not None:
+        s = torch.cat((s, sinks.float()[:, None, None].expand(-1, s.shape[1], 1)), dim=-1)
+        return torch.einsum("htj,jhd->thd", torch.softmax(s, dim=-1)[..., :-1], v)
     return torch.einsum("htj,jhd->thd", torch.softmax(s, dim=-1), v)
 
 
@@ -290,6 +295,109 @@ def biased_paged_attention(qkv, pool, page_table, ctx, *, num_heads, num_kv_head
         k, v = k.repeat_interleave(H // KV, dim=1), v.repeat_interleave(H // KV, dim=1)
         out[t0:t1] = _attend(q, k, v, n - (t1 - t0), scale, window, slopes).reshape(t1 - t0, -1).to(out.dtype)
     return out
+
+
+def paged_softmax_attention(q, pool, page_table, ctx, *, num_heads, num_kv_heads, key_dim, value_dim, scale, window=None, sinks=None, gate=None):
+    H, KV = num_heads, num_kv_heads
+    page_size = pool.shape[3]
+    out = torch.empty((q.shape[0], H * value_dim), dtype=q.dtype, device=q.device)
+    cu, lens = ctx.cu_tokens.tolist(), ctx.context_lens.tolist()
+    for r in range(len(lens)):
+        t0, t1, n = cu[r], cu[r + 1], lens[r]
+        pages = page_table[r, : -(-n // page_size)].long()
+        k = pool[pages, 0].float().permute(0, 2, 1, 3).reshape(-1, KV, pool.shape[4])[:n, :, :key_dim]
+        v = pool[pages, 1].float().permute(0, 2, 1, 3).reshape(-1, KV, pool.shape[4])[:n, :, :value_dim]
+        k, v = k.repeat_interleave(H // KV, dim=1), v.repeat_interleave(H // KV, dim=1)
+        o = _attend(q[t0:t1].float().view(t1 - t0, H, key_dim), k, v, n - (t1 - t0), scale, window, None, sinks).reshape(t1 - t0, -1)
+        if gate is not None:
+            o = o * torch.sigmoid(gate[t0:t1, : H * value_dim].float())
+        out[t0:t1] = o.to(out.dtype)
+    return out
+
+
+def head_prepare(proj, positions, *, heads, kv_heads, dim, value_dim=0, bias=None, q_weight=None, k_weight=None, eps=0.0, freq=None,
+                 warm=None, values_are_keys=False, pool=None, slot_map=None, out_dtype=None):
+    n = proj.shape[0]
+    cols = (heads + kv_heads) * dim + (0 if values_are_keys else kv_heads * value_dim)
+    row = proj[:, :cols].float()
+    if bias is not None:
+        row = row + bias.float()
+    q = row[:, : heads * dim].view(n, heads, dim)
+    k = row[:, heads * dim : (heads + kv_heads) * dim].view(n, kv_heads, dim)
+    v = k if values_are_keys else row[:, (heads + kv_heads) * dim :].view(n, kv_heads, value_dim)
+    if q_weight is not None:
+        q = q / torch.sqrt(q.pow(2).mean(-1, keepdim=True) + eps) * q_weight.float()
+        if kv_heads:
+            k = k / torch.sqrt(k.pow(2).mean(-1, keepdim=True) + eps) * k_weight.float()
+    if freq is not None:
+        half = freq.numel()
+        angle = positions.float()[:, None] * freq.float()[None, :]
+        c, s_ = angle.cos()[:, None, :], angle.sin()[:, None, :]
+
+        def turn(x):
+            a, b = x[..., :half], x[..., half : 2 * half]
+            return torch.cat((a * c - b * s_, b * c + a * s_, x[..., 2 * half :]), dim=-1)
+
+        q, k = turn(q), (turn(k) if kv_heads else k)
+    if warm:
+        coef, every = warm
+        q = q * (1.0 + coef * torch.log(torch.div(positions + 1, every, rounding_mode="floor").float() + 1.0))[:, None, None]
+    if kv_heads:
+        out_dtype = pool.dtype
+        page_size = pool.shape[3]
+        page, off = (slot_map // page_size).long(), (slot_map % page_size).long()
+        pool[page, 0, :, off, :dim] = k.to(pool.dtype)
+        pool[page, 1, :, off, : v.shape[-1]] = v.to(pool.dtype)
+    return q.reshape(n, heads * dim).to(out_dtype or proj.dtype)
+
+
+def hyper_mix_norm(streams, update, read_in, weight, eps, rows=None, out_dtype=torch.float32):
+    S = streams.shape[0]
+    x = streams if rows is None else streams[:, rows.long()]
+    if update is not None:
+        tensors, factors = update.results()
+        y = sum(f * (t if rows is None else t[rows.long()]).float() for t, f in zip(tensors, factors))
+        x = torch.einsum("st,snw->tnw", update.mix.view(S, S).float(), x) + update.take.float().view(S, 1, 1) * y[None]
+        if rows is None:
+            streams.copy_(x)
+    u = x.sum(0) if read_in is None else torch.einsum("s,snw->nw", read_in.float(), x)
+    return (u * torch.rsqrt(u.pow(2).mean(-1, keepdim=True) + eps) * weight).to(out_dtype)
+
+
+def linear32(x, w):
+    return x.float() @ w.float().t()
+
+
+def gated_scan(q, k, v, z, z_bias, inv_tau, q_scale, states, state_slots, cu_tokens, num_requests, heads, dim, value_dim, max_query_len=0):
+    out = torch.empty((q.shape[0], heads, value_dim), dtype=torch.float32, device=q.device)
+    cu, slots = cu_tokens.tolist(), state_slots.tolist()
+    logits = z.float() + (z_bias.float() if z_bias is not None else 0.0)
+    alpha = torch.exp(inv_tau * torch.nn.functional.logsigmoid(logits)).view(-1, heads, dim)
+    for r in range(num_requests):
+        S = states[slots[r]].float()
+        for t in range(cu[r], cu[r + 1]):
+            S = alpha[t][:, :, None] * S + k[t].float().view(heads, dim)[:, :, None] * v[t].float().view(heads, value_dim)[:, None, :]
+            out[t] = torch.einsum("hdv,hd->hv", S, q[t].float().view(heads, dim) * q_scale)
+        states[slots[r]] = S
+    return out
+
+
+def expert_gated_act(x, experts, ff, shared_ff, limit, shared_limit, slope, *, weights=None, ids=None, table=None):
+    n = x.shape[0]
+    xf = x.float()
+    if weights is None:
+        top = table.shape[1]
+        weights = torch.zeros((n, experts + 1), dtype=torch.float32, device=x.device)
+        weights.scatter_(1, table[ids.long()].long(), 1.0 / top)
+        weights[:, experts] = 1.0
+    out = torch.zeros((n, experts * ff + shared_ff), dtype=torch.float32, device=x.device)
+    for e in range(experts + int(shared_ff > 0)):
+        width, lim = (ff, limit) if e < experts else (shared_ff, shared_limit)
+        base = e * 2 * ff
+        g = xf[:, base : base + width].clamp(max=lim)
+        u = xf[:, base + width : base + 2 * width].clamp(min=-lim, max=lim)
+        out[:, e * ff : e * ff + width] = g * torch.sigmoid(slope * g) * (u + 1.0) * weights[:, e : e + 1]
+    return out.to(x.dtype)
 
 
 def qk_prepare(proj, positions, *, heads, kv_heads, dim, value_dim=0, freq=None, q_weight=None, k_weight=None, eps=0.0, k_scale=1.0,
@@ -368,10 +476,12 @@ def retention_scan(q, k, v, decay, states, state_slots, cu_tokens, num_requests,
     return out
 
 
-def head_norm_gate(o, gate, eps, kind="silu", out_dtype=torch.float32):
+def head_norm_gate(o, gate, eps, kind="silu", out_dtype=torch.float32, weight=None):
     y = o.float()
     if eps is not None:
         y = y / torch.sqrt(y.pow(2).mean(-1, keepdim=True) + eps)
+    if weight is not None:
+        y = y * weight.float()
     y = y.reshape(o.shape[0], -1)
     if gate is not None:
         z = gate.float()
@@ -420,6 +530,12 @@ def branch_sum_rmsnorm(pending, resid, weight, eps, out_dtype):
 
 
 ALL = (
+    "paged_softmax_attention",
+    "head_prepare",
+    "hyper_mix_norm",
+    "linear32",
+    "gated_scan",
+    "expert_gated_act",
     "branch_sum_rmsnorm",
     "qk_prepare",
     "sigmoid_attention",

@@ -115,8 +115,11 @@ def test_one_key_or_the_sink_decides(news, dtype, general, monkeypatch):
         targets = [0 if back is None else max(0, p - back) for p in positions]
         q = torch.stack([code[t] * 66.0 for t in targets]).repeat(1, H).to(DEV).to(dtype)
         want = torch.stack([vals[owner[i]][targets[i]].repeat_interleave(H // KV, dim=0).reshape(-1) for i in range(len(targets))])
-        for sink, share in ((None, 1.0), (30.0, 1.0), (66.0, 0.5), (90.0, 0.0)):
+        # the score of the chosen key as the rounded operands give it (66 in 32-bit, within a half of it in bfloat16)
+        score = (q[:, :D].float().cpu() * torch.stack([code[t] for t in targets]).to(dtype).float()).sum(-1, keepdim=True)
+        for sink in (None, 30.0, 66.0, 90.0):
             sinks = None if sink is None else torch.full((H,), sink, device=DEV)
+            share = 1.0 if sink is None else torch.sigmoid(score - sink)
             out = ops.paged_softmax_attention(q, pool, table, ctx, num_heads=H, num_kv_heads=KV, key_dim=D, value_dim=V, scale=1.0, sinks=sinks)
             err = float((out.float().cpu() - share * want.to(dtype).float()).abs().max())
             assert err <= (2e-4 if dtype == torch.float32 else 4e-2), f"key {back} back, sink {sink}: off by {err:.3e}"

@@ -14,7 +14,7 @@ cache of the live requests) to its time; ``points`` holds decode at batch 1 and 
 Peaks come from MEASURED_PEAKS.json beside this file when present, else from an earlier
 measurement on the same pool (and the line says which).
 
-``python bench.py --design nurolorn-small|nurolorn-1b|kafepel-small|kafepel-1b`` prints, instead of the line, prefill and decode
+``python bench.py --design nurolorn-small|nurolorn-1b|kafepel-small|kafepel-1b|nudodra-small|nudodra-1b`` prints, instead of the line, prefill and decode
 throughput of that configuration beside a Llama of equal width, depth and feed-forward size, and the design's kernels against
 their rooflines.
 
@@ -218,8 +218,13 @@ def design_comparison(args) -> int:
     dcfg = arch.config_class.from_dict(design)
     entries = len(arch.plan(dcfg).schedule)
     width, vocab = design["width"], design["vocab"]
-    ff = next(x["mlp"]["ff"] for x in design["layers"] if x.get("mlp") and "ff" in x["mlp"])
-    gated = design["architecture"] == "Kafepel"  # its dense feed-forward has three matrices, like the twin's
+    nudodra = design["architecture"] == "Nudodra"
+    if nudodra:  # no dense feed-forward: the twin's has the size of what a token uses (its chosen experts and the shared one)
+        moe = next(x["mlp"] for x in design["layers"] if x.get("mlp"))
+        ff = moe["router"]["top"] * moe["expert"]["ff"] + (moe["shared"]["ff"] if moe.get("shared") else 0)
+    else:
+        ff = next(x["mlp"]["ff"] for x in design["layers"] if x.get("mlp") and "ff" in x["mlp"])
+    gated = design["architecture"] in ("Kafepel", "Nudodra")  # their feed-forwards have three matrices, like the twin's
     twin = {
         "architectures": ["LlamaForCausalLM"], "model_type": "llama", "hidden_act": "silu", "rope_theta": 10000.0, "rms_norm_eps": 1e-5,
         "tie_word_embeddings": False, "vocab_size": vocab, "hidden_size": width, "intermediate_size": ff if gated else (ff * 2 // 3 + 63) // 64 * 64,
@@ -249,7 +254,10 @@ def design_comparison(args) -> int:
         return torch.randint(0, vocab, (n,), generator=g).tolist()
 
     out = {"design": args.design, "peaks_from": peaks_from, "models": {}}
-    for name, cfg_dict in ((args.design, design), ("llama-twin", twin)):
+    compared = [(args.design, design), ("llama-twin", twin)]
+    if nudodra:  # the closest design the engine has: side-by-side mixers and a routed feed-forward at the same sizes
+        compared.insert(1, (args.design.replace("nudodra", "kafepel"), dict(PRESETS[args.design.replace("nudodra", "kafepel")])))
+    for name, cfg_dict in compared:
         a = architecture_of(cfg_dict)
         model = random_model(a.config_class.from_dict(cfg_dict), 0, "bfloat16", device)
         cache = CacheManager(model.cache_specs(), model.plan.schedule, page_size=16, num_pages=8 * 200 + 64, max_requests=8,
@@ -321,8 +329,8 @@ def design_comparison(args) -> int:
 
     bf = torch.bfloat16
     kernels = {}
-    if design["architecture"] == "Kafepel":
-        _kafepel_kernels(design, twin, ops, torch, timed, ctx_for, i32, hbm, tensor, device)
+    if design["architecture"] in ("Kafepel", "Nudodra"):
+        (_nudodra_kernels if nudodra else _kafepel_kernels)(design, twin, ops, torch, timed, ctx_for, i32, hbm, tensor, device)
         out["kernels"] = kernels
         out["peaks"] = {"hbm_gbs": peaks["hbm_gbs"], "bf16_tflops": peaks["bf16_tflops"]}
         print(json.dumps(out, indent=1))
@@ -464,6 +472,84 @@ def _kafepel_kernels(design, twin, ops, torch, timed, ctx_for, i32, hbm, tensor,
         hbm(f"llama_swiglu_{label}", us, n * twin["intermediate_size"] * 6)
 
 
+def _nudodra_kernels(design, twin, ops, torch, timed, ctx_for, i32, hbm, tensor, device) -> None:
+    """The Nudodra design's own kernels, alone, at the preset's sizes: one request of 2,048 prompt tokens, and 8 decoding
+    requests of 2,048 cached tokens; beside each the like kernel of the Kafepel design (the closest one the engine has) at
+    the same sizes."""
+    bf = torch.bfloat16
+    par = next(x["mixer"] for x in design["layers"] if x["type"] == "parallel")
+    A, R = par["left"], par["right"]
+    moe = next(x["mlp"] for x in design["layers"] if x["mlp"])
+    width, S = design["width"], design.get("streams") or 1
+    H, KV, D, V = A["heads"], A["kv_heads"], A["dim"], A["vdim"]
+    for label, qs, cs in (("prefill_2048", [2048], [2048]), ("decode_8x2048", [1] * 8, [2048] * 8)):
+        ctx, table, slots, pages = ctx_for(qs, cs)
+        n = ctx.num_tokens
+        pairs = sum(q * c - q * (q - 1) // 2 for q, c in zip(qs, cs))
+        prefill = label.startswith("prefill")
+        pool = torch.randn(pages, 2, KV, 16, max(D, V), device=device).to(bf)
+        q = (torch.randn(n, H * D, device=device) * 0.3).to(bf)
+        sinks, gate = torch.zeros(H, device=device), torch.randn(n, H * V, device=device)
+        kw = dict(num_heads=H, num_kv_heads=KV, key_dim=D, value_dim=V, scale=A["scale"])
+        cache_bytes = sum(cs) * KV * (D + V) * 2 + n * H * (D + V) * 2
+        for name, more in (("sink_attention", dict(sinks=sinks)), ("gated_attention", dict(gate=gate))):
+            us = timed(lambda: ops.paged_softmax_attention(q, pool, table, ctx, **kw, **more))
+            (tensor if prefill else hbm)(f"{name}_{label}", us, 2.0 * pairs * H * (D + V) if prefill else cache_bytes, like="sigmoid_attention")
+        bias, mix = torch.zeros(H, device=device), torch.randn(H, H, device=device)
+        us = timed(lambda: ops.sigmoid_attention(q, pool, table, ctx, **kw, softcap=30.0, head_bias=bias, head_mix=mix))
+        (tensor if prefill else hbm)(f"kafepel_sigmoid_attention_{label}", us, 2.0 * pairs * H * (D + V) if prefill else cache_bytes)
+        # the heads' preparation (bias, per-head norms, rotation, cache write) beside Kafepel's (norms over whole projections)
+        proj = torch.randn(n, (H + KV) * D + KV * V, device=device)
+        freq = torch.rand(A["rot"]["dims"] // 2, device=device)
+        b_in, qw, kw_ = torch.randn((H + KV) * D, device=device), torch.ones(D, device=device), torch.ones(D, device=device)
+        us = timed(lambda: ops.head_prepare(proj, ctx.positions, heads=H, kv_heads=KV, dim=D, value_dim=V, bias=b_in, q_weight=qw, k_weight=kw_,
+                                            eps=1e-6, freq=freq, values_are_keys=True, pool=pool, slot_map=slots))
+        hbm(f"head_prepare_{label}", us, n * ((H + KV) * D * 4 + (H + 2 * KV) * D * 2), like="qk_prepare")
+        qwk, kwk = torch.ones(H * D, device=device), torch.ones(KV * D, device=device)
+        us = timed(lambda: ops.qk_prepare(proj, ctx.positions, heads=H, kv_heads=KV, dim=D, value_dim=V, freq=freq, q_weight=qwk, k_weight=kwk,
+                                          eps=1e-6, pool=pool, slot_map=slots))
+        hbm(f"kafepel_qk_prepare_{label}", us, n * ((H + KV) * D + KV * V) * (4 + 2))
+        # the recurrence: decays per channel and token beside Kafepel's fixed decay per head
+        RH, RD, RV = R["heads"], R["dim"], R["vdim"]
+        rq, rk, rz = (torch.randn(n, RH * RD, device=device) for _ in range(3))
+        rv = torch.randn(n, RH * RV, device=device)
+        zb = torch.full((RH * RD,), 3.0, device=device)
+        states, sl = torch.zeros(8, RH, RD, RV, device=device), i32(list(range(len(qs))))
+        us = timed(lambda: ops.gated_scan(rq, rk, rv, rz, zb, 1.0 / R["tau"], RD ** -0.5, states, sl, ctx.cu_tokens, len(qs), RH, RD, RV, max(qs)))
+        scan_bytes = n * RH * (3 * RD + 2 * RV) * 4 + 2 * len(qs) * RH * RD * RV * 4
+        hbm(f"gated_scan_{label}", us, scan_bytes, like="retention_scan")
+        decay = torch.full((RH,), 0.97, device=device)
+        us = timed(lambda: ops.retention_scan(rq, rk, rv, decay, states, sl, ctx.cu_tokens, len(qs), RH, RD, RV, max(qs)))
+        hbm(f"kafepel_retention_scan_{label}", us, n * RH * (2 * RD + 2 * RV) * 4 + 2 * len(qs) * RH * RD * RV * 4)
+        o, g2, wn = torch.randn(n, RH, RV, device=device), torch.randn(n, RH * RV, device=device), torch.ones(RV, device=device)
+        us = timed(lambda: ops.head_norm_gate(o, g2, 1e-6, "silu", bf, weight=wn))
+        hbm(f"head_norm_gate_{label}", us, n * RH * RV * (4 + 4 + 2), like="head_norm_gate (the same kernel)")
+        # the stream's copies: update, read-in and norm in one pass, beside Kafepel's meeting of branches with sum and norm
+        X = torch.randn(S, n, width, device=device)
+        a, b, wd = torch.randn(n, width, device=device), torch.randn(n, width, device=device), torch.ones(width, device=device)
+        upd = ops.StreamUpdate(ops.WeightedSum([a, b], [0.6, 0.5]), torch.eye(S, device=device).contiguous(), torch.ones(S, device=device))
+        rin = torch.ones(S, device=device)
+        us = timed(lambda: ops.hyper_mix_norm(X, upd, rin, wd, 1e-6, out_dtype=bf))
+        hbm(f"hyper_mix_norm_{label}", us, n * width * (2 * S * 4 + 2 * 4 + 2), like="branch_sum_norm")
+        resid = torch.randn(n, width, device=device)
+        pend = ops.BranchSum([a, b], [wd, wd], 1e-6, 0.5)
+        us = timed(lambda: ops.branch_sum_rmsnorm(pend, resid, wd, 1e-6, bf))
+        hbm(f"kafepel_branch_sum_norm_{label}", us, n * width * (4 * 4 + 2))
+        # the experts' activation with the table's weights beside Kafepel's with the router's
+        E, top, eff, sff = moe["router"]["experts"], moe["router"]["top"], moe["expert"]["ff"], moe["shared"]["ff"]
+        up2 = torch.randn(n, 2 * (E * eff + sff), device=device).to(bf)
+        tab = torch.rand(design["vocab"], E, device=device).argsort(dim=1)[:, :top].to(torch.int32).contiguous()
+        ids = torch.randint(0, design["vocab"], (n,), device=device, dtype=torch.int32)
+        us = timed(lambda: ops.expert_gated_act(up2, E, eff, sff, 7.0, 7.0, 1.702, ids=ids, table=tab))
+        hbm(f"expert_gated_act_{label}", us, n * ((top * eff + sff) * 4 + (E * eff + sff) * 2), like="expert_act_scale")
+        up1 = torch.randn(n, E * eff + sff, device=device).to(bf)
+        wts = torch.zeros(n, E + 1, device=device)
+        wts.scatter_(1, tab[ids.long()].long(), 1.0 / top)
+        wts[:, E] = 1.0
+        us = timed(lambda: ops.expert_act_scale(up1, wts, E, eff, "relu2"))
+        hbm(f"kafepel_expert_act_scale_{label}", us, n * ((top * eff + sff) * 2 + (E * eff + sff) * 2))
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -476,8 +562,8 @@ def main() -> int:
                          "fixed number of pages, with preemption")
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the configuration has (recorded in config)")
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 and 64, the end-to-end run and the kernel table")
-    ap.add_argument("--design", choices=["nurolorn-small", "nurolorn-1b", "kafepel-small", "kafepel-1b"], default=None,
-                    help="instead of the one line: prefill and decode throughput of a Nurolorn or Kafepel configuration beside a Llama of "
+    ap.add_argument("--design", choices=["nurolorn-small", "nurolorn-1b", "kafepel-small", "kafepel-1b", "nudodra-small", "nudodra-1b"], default=None,
+                    help="instead of the one line: prefill and decode throughput of a Nurolorn, Kafepel or Nudodra configuration beside a Llama of "
                          "equal width, depth and feed-forward size, and the design's own kernels against their rooflines")
     ap.add_argument("--sweep", action="store_true",
                     help="instead of the one line: a table of decode steps over batch sizes and context lengths and of prefills over prompt lengths")

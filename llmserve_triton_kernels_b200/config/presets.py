@@ -56,7 +56,31 @@ def _kafepel(width: int, layers: int, heads: int, kv_heads: int, ff: int, expert
     }
 
 
+def _nudodra(width: int, pattern: str, heads: int, kv_heads: int, experts: int, top: int, expert_ff: int, shared_ff: int, streams: int = 4,
+             vocab: int = 32000) -> dict:
+    """``pattern``: one letter a layer, P side-by-side mixers, A attention with keys and values of its own, a attention that
+    reads the pages of the last A in front of it.  Heads of 64 lanes; the recurrent branch has half as many heads with keys
+    of 64 and values of 128 lanes and a decay product of inner size 64; every layer has the table-routed feed-forward."""
+    head = 64
+    left = {"heads": heads, "kv_heads": kv_heads, "dim": head, "vdim": head, "scale": head ** -0.5, "rot": {"base": 10000.0, "dims": head // 2}}
+    right = {"heads": heads // 2, "dim": head, "vdim": 2 * head, "tau": 16.0, "rank": 64}
+    attention = {"heads": heads, "kv_heads": kv_heads, "dim": head, "vdim": head, "scale": head ** -0.5, "q_temp": {"coef": 0.1, "every": 1024}}
+    moe = {"kind": "moe", "router": {"experts": experts, "top": top}, "expert": {"ff": expert_ff, "limit": 7.0}, "shared": {"ff": shared_ff, "limit": 7.0}}
+    layers, last = [], None
+    for i, c in enumerate(pattern):
+        if c == "P":
+            layers.append({"type": "parallel", "mixer": {"left": left, "right": right, "left_scale": 0.6, "right_scale": 0.5}, "mlp": moe})
+        else:
+            mixer = dict(attention) if c == "A" else {**attention, "kv_from": last}
+            last = i if c == "A" else last
+            layers.append({"type": "attention", "mixer": mixer, "mlp": moe})
+    return {"architecture": "Nudodra", "vocab": vocab, "width": width, "streams": streams, "norm": {"eps": 1e-6}, "layers": layers}
+
+
 PRESETS: dict[str, dict] = {
+    # Nudodra at the sizes of the Kafepel presets below (the design has no published sizes)
+    "nudodra-small": _nudodra(1024, "PAaPAaPP", 16, 4, 16, 2, 512, 1024),
+    "nudodra-1b": _nudodra(2048, "PAaPAaPAaPPA", 32, 8, 32, 4, 704, 1408),
     # Kafepel at sizes that resemble real layers (the design has no published sizes)
     "kafepel-small": _kafepel(1024, 8, 16, 4, 2816, 16, 2, 512, 1024),
     "kafepel-1b": _kafepel(2048, 12, 32, 8, 5632, 32, 4, 704, 1408),

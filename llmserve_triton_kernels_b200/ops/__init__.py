@@ -67,7 +67,7 @@ _SIGNATURES = {
     "llm_embed_copies": [_vp, _vp, _i, _vp, _i, _i, _i, _i, _vp],
     "llm_hyper_mix_norm": [_vp, _vp, _vp, _vp, _vp, _f, _f, _f, _f, _i, _vp, _vp, _vp, _vp, _f, _vp, _vp, _i, _i, _i, _i, _i, _vp],
     "llm_head_prepare": [_vp, _i, _i, _vp, _vp, _i, _vp, _i, _vp, _i, _i, _vp, _vp, _f, _i, _vp, _i, _vp, _f, _i, _i, _i, _i, _i, _i, _i, _vp],
-    "llm_gated_scan": [_vp, _i, _vp, _i, _vp, _i, _i, _vp, _i, _vp, _f, _f, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
+    "llm_gated_scan": [_vp, _i, _vp, _i, _vp, _i, _i, _vp, _i, _vp, _f, _f, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _i, _vp],
     "llm_expert_gated_act": [_vp, _i, _vp, _i, _i, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _f, _f, _vp],
     "llm_router": [_vp, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _i, _vp],
     "llm_route_topk": [_vp, _i, _vp, _vp, _i, _i, _i, _f, _i, _i, _vp],
@@ -1329,7 +1329,8 @@ def gated_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, z: torch.Tenso
     """``S = diag(alpha_t) S + k_t v_t^T``, ``o_t = S^T (q_scale * q_t)`` per head over every request's new tokens, with a
     decay per key channel that the token chooses: ``alpha_t = sigmoid(z_t + z_bias) ^ inv_tau``.  From and to
     ``states[state_slots[r]]`` (``[slots, heads, dim, value_dim]`` float32).  ``q, k, z [N, heads * dim]`` float32 and
-    ``v [N, heads * value_dim]`` (views with a row pitch will do).  Returns ``o [N, heads, value_dim]`` float32."""
+    ``v [N, heads * value_dim]`` (views with a row pitch will do).  Returns ``o [N, heads, value_dim]`` float32.  Long
+    requests are shared out over several CTAs in stretches, as in :func:`retention_scan` (the same kernel walks both)."""
     for t in (q, k, z):
         _need(t.dtype == torch.float32 and t.stride(1) == 1 and t.shape[1] == heads * dim, "gated_scan: q, k and the decays' logits are float32 [N, heads * dim]")
     _need(v.stride(1) == 1 and v.shape[1] == heads * value_dim, "gated_scan: v [N, heads * value_dim]")
@@ -1339,9 +1340,14 @@ def gated_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, z: torch.Tenso
     _i32(cu_tokens, "cu_tokens")
     out = torch.empty((q.shape[0], heads, value_dim), dtype=torch.float32, device=q.device)
     few = 0 < int(max_query_len) <= 16
+    stretches = _scan_stretches(few, dim, value_dim, heads, int(num_requests), int(max_query_len))
+    scratch = None
+    if stretches > 1:  # the stretches' end states, start states and products of decays
+        scratch = torch.empty((int(num_requests) * stretches * heads * (2 * dim * value_dim + dim),), dtype=torch.float32, device=q.device)
     code = _launch("llm_gated_scan", _ptr(q), q.stride(0), _ptr(k), k.stride(0), _ptr(v), _code(v.dtype), v.stride(0), _ptr(z), z.stride(0),
                    _ptr(z_bias), float(inv_tau), float(q_scale), _ptr(states), _ptr(state_slots), _ptr(cu_tokens), _ptr(out), int(num_requests),
-                   heads, dim, value_dim, int(few), _stream())
+                   heads, dim, value_dim, stretches, _ptr(scratch), int(few), _stream())
+    add_launches(2 * int(stretches > 1))
     _check(code, "gated_scan")
     return out
 
@@ -1470,6 +1476,13 @@ def sigmoid_attention(q: torch.Tensor, pool: torch.Tensor, page_table: torch.Ten
 _RETENTION_MIN_STRETCH = 64  # tokens a stretch of a long request has at least
 
 
+def _scan_stretches(few: bool, dim: int, value_dim: int, heads: int, requests: int, max_query_len: int) -> int:
+    """Into how many stretches the scans (csrc/retention.cu) cut a long request, so that the GPU has CTAs enough."""
+    cols = 16 if few else 64 if dim <= 64 else 32 if dim <= 128 else 16  # columns of the state that one CTA owns
+    ctas = -(-value_dim // cols) * heads * requests
+    return max(1, min(8, max_query_len // _RETENTION_MIN_STRETCH, -(-4 * _sm_count() // ctas), 65535 // max(1, requests)))
+
+
 def retention_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: torch.Tensor, states: torch.Tensor,
                    state_slots: torch.Tensor, cu_tokens: torch.Tensor, num_requests: int, heads: int, dim: int, value_dim: int,
                    max_query_len: int = 0) -> torch.Tensor:
@@ -1487,9 +1500,7 @@ def retention_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: tor
     _i32(cu_tokens, "cu_tokens")
     out = torch.empty((q.shape[0], heads, value_dim), dtype=torch.float32, device=q.device)
     few = 0 < int(max_query_len) <= 16  # a decode step, or portions of a few tokens
-    cols = 16 if few else 64 if dim <= 64 else 32 if dim <= 128 else 16  # columns of the state that one CTA owns (csrc/retention.cu)
-    ctas = -(-value_dim // cols) * heads * int(num_requests)
-    stretches = max(1, min(8, int(max_query_len) // _RETENTION_MIN_STRETCH, -(-4 * _sm_count() // ctas), 65535 // max(1, int(num_requests))))
+    stretches = _scan_stretches(few, dim, value_dim, heads, int(num_requests), int(max_query_len))
     scratch = None
     if stretches > 1:
         scratch = torch.empty((2, int(num_requests) * stretches, heads, dim, value_dim), dtype=torch.float32, device=q.device)

@@ -160,6 +160,31 @@ def test_gated_scan_against_plain_and_across_ways_of_cutting(H, D, V, v_dtype):
     assert torch.equal(o3, o1) and torch.equal(s3, s1), "the recurrence depends on how the tokens were cut"
 
 
+@pytest.mark.parametrize("H,D,V", [(2, 48, 64), (1, 20, 24), (2, 128, 40), (1, 256, 16), (16, 64, 128)])
+def test_gated_scan_of_long_requests_shared_out_in_stretches(H, D, V):
+    """Requests long enough that the kernel cuts them into stretches for several CTAs (each walked from a zero state, the
+    start states found from the end states and the stretches' products of decays, the missing term added afterwards),
+    beside a short one, against the plain statement.  Some channels hardly forget and some forget at once."""
+    ops = _ops()
+    torch.manual_seed(D + V)
+    lens = [900, 3, 517, 130]
+    N = sum(lens)
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device=DEV)
+    slots = torch.tensor([1, 4, 0, 2], dtype=torch.int32, device=DEV)
+    wide = torch.randn(N, 3 * H * D + H * V + 4, device=DEV)
+    q, k, z = wide[:, : H * D], wide[:, H * D : 2 * H * D], wide[:, 2 * H * D : 3 * H * D] * 2.0
+    v = wide[:, 3 * H * D : 3 * H * D + H * V]
+    zb = torch.randn(H * D, device=DEV) * 3.0 + 4.0
+    states0 = torch.randn(5, H, D, V, device=DEV)
+    args = (zb, 1.0 / 16.0, D ** -0.5)
+    s1, s2 = states0.clone(), states0.clone()
+    o1 = ops.gated_scan(q, k, v, z, *args, s1, slots, cu, 4, H, D, V, max_query_len=max(lens))
+    o2 = plain_ops.gated_scan(q, k, v, z, *args, s2, slots, cu, 4, H, D, V)
+    close(o1, o2, 1e-4, "outputs")
+    close(s1, s2, 1e-4, "states")
+    assert torch.equal(s1[3], states0[3]), "a slot that no request names was written"
+
+
 @pytest.mark.parametrize("out_dtype,tol", [(torch.float32, 1e-5), (torch.bfloat16, 1e-2)])
 @pytest.mark.parametrize("S,W,results", [(1, 40, 1), (2, 192, 2), (3, 33, 1), (4, 1024, 2), (8, 2048, 4), (5, 7, 3)])
 def test_hyper_mix_norm_against_plain(S, W, results, out_dtype, tol):

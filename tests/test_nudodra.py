@@ -36,12 +36,22 @@ def _judge(errors, dtype: str, what: str):
 
 def check(got, expected, dtype: str, what: str = ""):
     errors = []
+    scale = _scale_of([expected[req.split("#")[0]][pos] for req, pos in got], dtype)
     for (req, pos), row in sorted(got.items()):
         ref = expected[req.split("#")[0]][pos].float()
         assert torch.isfinite(row).all(), f"{what}: non-finite logits at request {req!r} position {pos}"
         d = row - ref
-        errors.append((req, pos, float((d - d.mean()).pow(2).mean().sqrt() / ref.pow(2).mean().sqrt().clamp_min(1e-6))))
+        errors.append((req, pos, float((d - d.mean()).pow(2).mean().sqrt() / ref.pow(2).mean().sqrt().clamp_min(scale))))
     _judge(errors, dtype, what)
+
+
+def _scale_of(rows, dtype: str) -> float:
+    """What a row's error is divided by, at least.  In 32-bit: next to nothing, so every row is measured against its own
+    size.  In bfloat16 a row's rounding error follows the size of the activations it came through, not its own size: a row
+    whose logits happen to be small is measured against the root mean square of all rows compared."""
+    if dtype == "float32":
+        return 1e-6
+    return float(torch.stack([r.double().pow(2).mean() for r in rows]).mean().sqrt())
 
 
 def expected_of(cfg, tensors, requests):
@@ -415,13 +425,14 @@ def _replay_trace(cfg, seed=31):
 def _check_replay(got, cfg, tensors, flat, dtype):
     done, errors = {}, []
     assert got
+    for req in {req for req, _ in got}:
+        if tuple(flat[req]) not in done:
+            done[tuple(flat[req])] = plain_nudodra.forward(cfg, tensors, flat[req])
+    scale = _scale_of([done[tuple(flat[req])][pos] for req, pos in got], dtype)
     for (req, pos), row in sorted(got.items()):
-        key = tuple(flat[req])
-        if key not in done:
-            done[key] = plain_nudodra.forward(cfg, tensors, flat[req])
-        ref = done[key][pos]
+        ref = done[tuple(flat[req])][pos]
         d = torch.from_numpy(row.copy()).double() - ref
-        errors.append((req, pos, float((d - d.mean()).pow(2).mean().sqrt() / ref.pow(2).mean().sqrt().clamp_min(1e-6))))
+        errors.append((req, pos, float((d - d.mean()).pow(2).mean().sqrt() / ref.pow(2).mean().sqrt().clamp_min(scale))))
     _judge(errors, dtype, "replay")
 
 

@@ -63,13 +63,13 @@ def _nudodra(width: int, pattern: str, heads: int, kv_heads: int, experts: int, 
     of 64 and values of 128 lanes and a decay product of inner size 64; every layer has the table-routed feed-forward."""
     head = 64
     left = {"heads": heads, "kv_heads": kv_heads, "dim": head, "vdim": head, "scale": head ** -0.5, "rot": {"base": 10000.0, "dims": head // 2}}
-    right = {"heads": heads // 2, "dim": head, "vdim": 2 * head, "tau": 16.0, "rank": 64}
+    right = {"heads": heads // 2, "dim": head, "vdim": 2 * head, "tau": 8.0, "rank": 64}
     attention = {"heads": heads, "kv_heads": kv_heads, "dim": head, "vdim": head, "scale": head ** -0.5, "q_temp": {"coef": 0.1, "every": 1024}}
     moe = {"kind": "moe", "router": {"experts": experts, "top": top}, "expert": {"ff": expert_ff, "limit": 7.0}, "shared": {"ff": shared_ff, "limit": 7.0}}
     layers, last = [], None
     for i, c in enumerate(pattern):
         if c == "P":
-            layers.append({"type": "parallel", "mixer": {"left": left, "right": right, "left_scale": 0.6, "right_scale": 0.5}, "mlp": moe})
+            layers.append({"type": "parallel", "mixer": {"left": left, "right": right, "left_scale": 0.7, "right_scale": 0.7}, "mlp": moe})
         else:
             mixer = dict(attention) if c == "A" else {**attention, "kv_from": last}
             last = i if c == "A" else last

@@ -69,8 +69,8 @@ ONES = config([
 ], vocab=61, width=64, eps=1e-6, streams=1)
 # more heads, many experts, four copies, keys wider than values, a head of 48 lanes on the tensor cores
 WIDE = config([
-    attention_layer(attention(12, 4, 48, 16, 0.15, coef=0.5, every=16), moe(37, 4, 6, 1.1, shared=10, shared_limit=2.0)),
-    parallel_layer(left(6, 3, 20, 0.22, dims=10), right(3, 40, 70, 16.0, rank=5), 0.6, 0.5, moe(6, 3, 10, 0.8)),
+    attention_layer(attention(12, 4, 48, 16, 0.15, coef=0.35, every=16), moe(37, 4, 6, 1.1, shared=10, shared_limit=2.0)),
+    parallel_layer(left(6, 3, 20, 0.22, dims=10), right(3, 40, 70, 12.0, rank=5), 0.55, 0.45, moe(6, 3, 10, 0.8)),
     attention_layer(attention(4, 4, 48, 16, 0.2, coef=0.2, every=7, kv_from=0), moe(2, 2, 24, 1.0)),
 ], vocab=128, width=96, eps=1e-5, streams=4)
 # no ``streams`` key: one plain residual stream, the contributions are simply added

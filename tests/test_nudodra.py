@@ -118,7 +118,7 @@ ALONE = {
     "gated_linear": configs.config([configs.parallel_layer(_TINY_LEFT, configs.right(3, 10, 14, 3.0, rank=4), 0.05, 1.4)], width=32),
     "gated_linear_wide": configs.config([configs.parallel_layer(_TINY_LEFT, configs.right(2, 40, 70, 20.0, rank=2), 0.05, 0.9)], width=32, streams=None),
     "attention": configs.config([configs.attention_layer(configs.attention(6, 2, 10, 6, 0.5, coef=0.9, every=4))], width=32),
-    "attention_48": configs.config([configs.attention_layer(configs.attention(6, 1, 48, 48, 0.2, coef=0.5, every=8))], width=32),
+    "attention_48": configs.config([configs.attention_layer(configs.attention(8, 2, 48, 48, 0.2, coef=0.3, every=8))], width=32),
     "shared_pages": configs.config([configs.attention_layer(configs.attention(2, 1, 8, 4, 0.5, coef=0.5, every=4)),
                                     configs.attention_layer(configs.attention(4, 1, 8, 4, 0.4, coef=0.8, every=2, kv_from=0))], width=32),
     "experts": configs.config([configs.attention_layer(configs.attention(1, 1, 4, 4, 0.5), configs.moe(7, 3, 9, 0.3, shared=11, shared_limit=0.15))], width=32),

@@ -15,7 +15,7 @@ from test_kafepel_kernels_gpu import DEV, _ops, close, paged_batch
 pytestmark = pytest.mark.gpu
 
 # heads, kv heads, key lanes, value lanes, rotated lanes, page size
-SHAPES = [(8, 2, 24, 40, 24, 16), (3, 1, 10, 6, 4, 8), (6, 1, 48, 48, 0, 16), (4, 4, 128, 128, 64, 4), (1, 1, 2, 1, 2, 1), (5, 5, 7, 3, 0, 3),
+SHAPES = [(8, 2, 24, 40, 24, 16), (3, 1, 10, 6, 4, 8), (6, 2, 48, 48, 0, 16), (4, 4, 128, 128, 64, 4), (1, 1, 2, 1, 2, 1), (5, 5, 7, 3, 0, 3),
           (4, 2, 64, 64, 16, 16), (12, 4, 16, 32, 8, 8)]
 
 
@@ -160,7 +160,7 @@ def test_gated_scan_against_plain_and_across_ways_of_cutting(H, D, V, v_dtype):
     assert torch.equal(o3, o1) and torch.equal(s3, s1), "the recurrence depends on how the tokens were cut"
 
 
-@pytest.mark.parametrize("H,D,V", [(2, 48, 64), (1, 20, 24), (2, 128, 40), (1, 256, 16), (16, 64, 128)])
+@pytest.mark.parametrize("H,D,V", [(2, 56, 64), (1, 20, 24), (2, 128, 40), (1, 256, 16), (16, 64, 128)])
 def test_gated_scan_of_long_requests_shared_out_in_stretches(H, D, V):
     """Requests long enough that the kernel cuts them into stretches for several CTAs (each walked from a zero state, the
     start states found from the end states and the stretches' products of decays, the missing term added afterwards),
@@ -176,7 +176,7 @@ def test_gated_scan_of_long_requests_shared_out_in_stretches(H, D, V):
     v = wide[:, 3 * H * D : 3 * H * D + H * V]
     zb = torch.randn(H * D, device=DEV) * 3.0 + 4.0
     states0 = torch.randn(5, H, D, V, device=DEV)
-    args = (zb, 1.0 / 16.0, D ** -0.5)
+    args = (zb, 1.0 / 12.0, D ** -0.5)
     s1, s2 = states0.clone(), states0.clone()
     o1 = ops.gated_scan(q, k, v, z, *args, s1, slots, cu, 4, H, D, V, max_query_len=max(lens))
     o2 = plain_ops.gated_scan(q, k, v, z, *args, s2, slots, cu, 4, H, D, V)
@@ -211,7 +211,7 @@ def test_hyper_mix_norm_against_plain(S, W, results, out_dtype, tol):
 
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.bfloat16, 1e-2)])
-@pytest.mark.parametrize("E,top,ff,fs", [(5, 2, 12, 20), (16, 2, 64, 96), (1, 1, 32, 0), (37, 4, 6, 10), (3, 3, 7, 5), (8, 1, 8, 8)])
+@pytest.mark.parametrize("E,top,ff,fs", [(5, 2, 12, 20), (16, 2, 48, 80), (1, 1, 32, 0), (37, 4, 6, 10), (3, 3, 7, 5), (8, 1, 8, 8)])
 def test_expert_activation_with_a_table_against_plain(E, top, ff, fs, dtype, tol):
     ops = _ops()
     torch.manual_seed(E * 10 + ff)

@@ -109,11 +109,31 @@ class PageGroup:
         """The request's table as int32 (released pages read 0); a view, not to be written."""
         return self._rows[req][: len(self.tables[req])]
 
+    @property
+    def releases(self) -> bool:
+        """Whether pages of this group go back to the pool while their request lives."""
+        return self.spec.window is not None or getattr(self.spec, "chunk", None) is not None
+
     def first_needed_page(self, length: int) -> int:
-        """Logical index of the first page that a query at position ``length`` or later reads."""
-        if self.spec.window is None:
-            return 0
-        return max(0, length - self.spec.window + 1) // self.page_size
+        """Logical index of the first page behind the kept first tokens that a query at position ``length`` or later
+        reads: the start of its window or of its block of positions, whichever is later."""
+        first = 0
+        if self.spec.window is not None:
+            first = max(0, length - self.spec.window + 1)
+        chunk = getattr(self.spec, "chunk", None)
+        if chunk:
+            first = max(first, (length // chunk) * chunk)
+        return first // self.page_size
+
+    def kept_pages(self) -> int:
+        """Pages at the head of every table that are never released: those that hold one of the kept first tokens."""
+        keep = getattr(self.spec, "keep_first", None) or 0
+        return -(-keep // self.page_size) if self.releases else 0
+
+    def span(self) -> int | None:
+        """The most positions behind a query that it reads (None: all of them)."""
+        spans = [s for s in (self.spec.window, getattr(self.spec, "chunk", None)) if s]
+        return min(spans) if spans else None
 
     def extra_pages(self, req, length: int, new_tokens: int) -> int:
         table = self.tables[req]
@@ -185,10 +205,10 @@ class CacheManager:
         is fed in portions of at most ``chunk`` tokens."""
         need = 0
         for g in self.groups:
-            if g.spec.window is None:
+            if not g.releases:
                 need = max(need, self.pages_for(tokens))
             else:
-                need = max(need, min(self.pages_for(tokens), self.pages_for(g.spec.window + chunk) + 1))
+                need = max(need, min(self.pages_for(tokens), self.pages_for(g.span() + chunk) + 1 + g.kept_pages()))
         return need
 
     @property
@@ -203,10 +223,10 @@ class CacheManager:
 
     def internal_fragmentation(self) -> float:
         """Share of held token places that hold no token (tails of last pages), over groups that keep all keys."""
-        held = sum(g.allocator.num_used for g in self.groups if g.spec.window is None) * self.page_size
+        held = sum(g.allocator.num_used for g in self.groups if not g.releases) * self.page_size
         if held == 0:
             return 0.0
-        used = sum(self.lengths.values()) * sum(1 for g in self.groups if g.spec.window is None)
+        used = sum(self.lengths.values()) * sum(1 for g in self.groups if not g.releases)
         return 1.0 - used / held
 
     def nbytes(self) -> int:
@@ -268,10 +288,10 @@ class CacheManager:
             self.lengths[req] += n
             length = self.lengths[req]
             for g in self.groups:
-                if g.spec.window is None:
+                if not g.releases:
                     continue
                 table = g.tables[req]
-                stale = [i for i in range(min(g.first_needed_page(length), len(table))) if table[i] != RELEASED]
+                stale = [i for i in range(g.kept_pages(), min(g.first_needed_page(length), len(table))) if table[i] != RELEASED]
                 g.allocator.free([table[i] for i in stale])
                 for i in stale:
                     g.release_page(req, i)

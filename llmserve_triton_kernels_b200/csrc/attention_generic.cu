@@ -7,7 +7,8 @@
 // the absolute key position, so the order of every addition depends only on the query's
 // position (and the window), never on how the tokens were cut into steps or batched.
 //
-// A query at position p of request r sees keys max(0, p - window + 1) .. p (window <= 0: from 0).
+// A query at position p of request r sees keys max(0, p - window + 1) .. p (window <= 0: from 0), with a window also the
+// keys below keep_first; with chunk > 0 only those from the start of its own block of chunk positions on.
 #include <type_traits>
 
 #include "attention_rows.cuh"
@@ -29,7 +30,9 @@ __global__ void __launch_bounds__(WARPS * 32) attention_rows_kernel(const RowsAr
     const int q_begin = a.cu_tokens[r], q_len = a.cu_tokens[r + 1] - q_begin;
     const int pos = a.ctx_lens[r] - q_len + (t - q_begin);
     const int kvh = h / (a.H / a.KV);
-    const int lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;
+    int lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;
+    if (a.chunk > 0) lo = max(lo, pos - pos % a.chunk);
+    const int kept = a.window > 0 ? min(a.keep_first, lo) : 0;  // keys [0, kept) are seen besides [lo, pos]
     const int dk = a.d0 + a.d1, dv = a.dv;
     const float slope = a.slopes ? a.slopes[h] : 0.f;
 
@@ -49,16 +52,20 @@ __global__ void __launch_bounds__(WARPS * 32) attention_rows_kernel(const RowsAr
     // a sink stands for a key of score sinks[h] and no value: the running maximum and sum start from it
     float m = a.sinks ? a.sinks[h] : -INFINITY, l = a.sinks ? 1.f : 0.f;
 
-    for (int c = (lo / 32) * 32; c <= pos; c += 32) {
+    const int c_lo = (lo / 32) * 32, c_kept = ((kept + 31) / 32) * 32;  // the chunks of the kept keys end before c_kept
+    for (int c = kept > 0 ? 0 : c_lo; c <= pos; c += 32) {
+        if (c >= c_kept && c < c_lo) c = c_lo;  // nothing is seen between the kept keys and the window
         const int j = c + lane;
-        const bool visible = j >= lo && j <= pos;
+        const bool visible = (j >= lo && j <= pos) || j < kept;
         float s = -INFINITY;
         if (visible) {
             const int page = table[j / a.page_size], off = j % a.page_size;
             const T* kp = a.keys + (long long)page * a.k_page + (long long)kvh * a.k_head + (long long)off * a.k_token;
             float dot = 0.f;
             for (int d = 0; d < dk; ++d) dot = fmaf(q_s[warp][d], to_float(kp[d]), dot);
-            s = dot * a.scale - slope * (float)(pos - j);
+            s = dot * a.scale;
+            if (a.softcap > 0.f) s = a.softcap * tanhf(s / a.softcap);
+            s -= slope * (float)(pos - j);
         }
         const float m_new = fmaxf(m, warp_max(s));  // finite: the chunk holds at least one visible key
         const float p = visible ? expf(s - m_new) : 0.f;
@@ -115,9 +122,9 @@ LLM_EXPORT int llm_attention_rows(const void* q0, long long q0_token, long long 
                                   const int* page_table, int table_width, const int* token_request, const int* cu_tokens,
                                   const int* ctx_lens, const float* slopes, int n_tokens, int H, int KV, int page_size,
                                   int window, float scale, const float* sinks, const float* gate, long long gate_token,
-                                  cudaStream_t stream) {
+                                  int keep_first, int chunk, float softcap, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
-    if (d0 <= 0 || d1 < 0 || d0 + d1 > MAX_DK || dv <= 0 || dv > MAX_DV || H <= 0 || KV <= 0 || H % KV || page_size <= 0 ||
+    if (keep_first < 0 || chunk < 0 || d0 <= 0 || d1 < 0 || d0 + d1 > MAX_DK || dv <= 0 || dv > MAX_DV || H <= 0 || KV <= 0 || H % KV || page_size <= 0 ||
         table_width <= 0 || (d1 > 0 && q1 == nullptr))
         return LLM_ERR_BAD_ARGUMENT;
     auto fill = [&](auto& a, auto* tag) {
@@ -132,7 +139,7 @@ LLM_EXPORT int llm_attention_rows(const void* q0, long long q0_token, long long 
         a.page_table = page_table; a.token_request = token_request; a.cu_tokens = cu_tokens; a.ctx_lens = ctx_lens;
         a.slopes = slopes;
         a.table_width = table_width; a.n_tokens = n_tokens; a.H = H; a.KV = KV; a.page_size = page_size; a.window = window;
-        a.scale = scale;
+        a.scale = scale; a.keep_first = keep_first; a.chunk = chunk; a.softcap = softcap;
         a.key_part = 0; a.keys1 = nullptr; a.k1_token = 0; a.fresh_d0 = 0; a.stats = nullptr;
         a.sinks = sinks; a.gate = gate; a.gate_token = gate_token;
     };
@@ -162,5 +169,5 @@ LLM_EXPORT int llm_attention_generic(const void* q, int q_stride, void* out, int
     const void* values = (const char*)pool + (size_t)KV * head * element;
     return llm_attention_rows(q, q_stride, D, D, nullptr, 0, 0, 0, out, out_stride, D, pool, page, head, D, values, page, head,
                               D, D, dtype, page_table, table_width, token_request, cu_tokens, ctx_lens, nullptr, n_tokens, H,
-                              KV, page_size, window, scale, nullptr, nullptr, 0, stream);
+                              KV, page_size, window, scale, nullptr, nullptr, 0, 0, 0, 0.f, stream);
 }

@@ -20,7 +20,12 @@ struct RowsArgs {
     const int *page_table, *token_request, *cu_tokens, *ctx_lens;
     const float* slopes;  // per query head: the score of key j for the query at position i loses slope * (i - j); null: none
     int table_width, n_tokens, H, KV, page_size, window;
+    // With a window, keys at positions below keep_first stay visible to every later query (0: none).  chunk > 0: a query
+    // sees only keys of its own block of `chunk` positions, counted from position 0.
+    int keep_first, chunk;
     float scale;
+    // > 0: a score s (scaled) becomes softcap * tanh(s / softcap) before the distance bias is taken off
+    float softcap;
     // Which keys: 0 all that a row sees; 1 only those cached before this step (positions before the request's first new
     // token); 2 only the step's own tokens, whose keys and values then lie token by token, not in pages: token i of the
     // flat batch at keys + i * k_token + head * k_head (lanes [0, fresh_d0)) and at keys1 + i * k1_token (the lanes

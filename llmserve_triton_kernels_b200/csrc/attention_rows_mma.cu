@@ -72,10 +72,17 @@ attention_rows_mma_kernel(const RowsArgs<bf16> a, int splits, float* __restrict_
     // the keys this tile's rows see, and this split's share of their tiles
     const int pos_min = first_pos + row0 / group, pos_max = first_pos + min(rows_total - 1, row0 + BM - 1) / group;
     int key_lo = a.window > 0 ? max(0, pos_min - a.window + 1) : 0, key_hi = pos_max;
+    if (a.chunk > 0) key_lo = max(key_lo, pos_min - pos_min % a.chunk);  // the oldest row's block of positions starts first
     if (a.key_part == 1) key_hi = min(key_hi, first_pos - 1);  // only what was cached before this step
     if (a.key_part == 2) key_lo = max(key_lo, first_pos);     // only the step's own tokens
-    const int j_first = (key_lo / BN) * BN;
-    const int n_tiles = key_hi >= j_first ? (key_hi - j_first) / BN + 1 : 0;
+    // with a window the keys below keep_first stay visible: their tiles come first, then the window's (one run from key 0
+    // where the two meet)
+    const int kf = (a.window > 0 && a.key_part == 0) ? a.keep_first : 0;
+    int j_first = (key_lo / BN) * BN;
+    int kept_tiles = (min(kf, key_lo) + BN - 1) / BN;
+    if (kept_tiles * BN >= j_first) { j_first = 0; kept_tiles = 0; }
+    const int n_tiles = (key_hi >= j_first ? (key_hi - j_first) / BN + 1 : 0) + kept_tiles;
+    auto tile_start = [&](int t) { return t < kept_tiles ? t * BN : j_first + (t - kept_tiles) * BN; };
     const int per = (n_tiles + splits - 1) / splits;
     const int t_begin = split * per, t_end = min(n_tiles, t_begin + per);
 
@@ -95,7 +102,7 @@ attention_rows_mma_kernel(const RowsArgs<bf16> a, int splits, float* __restrict_
     pdl_wait();  // the queries and the newest cached rows are the work of the kernels in front
     // eight lanes a key (128 bytes of its row a pass), sixteen keys a pass of the CTA: a key's page is looked up once
     auto load_tile = [&](int t, int stage) {
-        const int j0 = j_first + t * BN, sub = tid & 7;
+        const int j0 = tile_start(t), sub = tid & 7;
         bf16* kd = Ks + stage * BN * kp;
         bf16* vd = Vs + stage * BN * vp;
         for (int key = tid >> 3; key < BN; key += THREADS / 8) {
@@ -147,17 +154,19 @@ attention_rows_mma_kernel(const RowsArgs<bf16> a, int splits, float* __restrict_
         const int R = min(row0 + warp * 16 + (lane >> 2) + 8 * e, rows_total - 1);
         pos[e] = first_pos + R / group;
         lo[e] = a.window > 0 ? max(0, pos[e] - a.window + 1) : 0;
+        if (a.chunk > 0) lo[e] = max(lo[e], pos[e] - pos[e] % a.chunk);
         if (a.key_part == 2) lo[e] = max(lo[e], first_pos);
         hi[e] = a.key_part == 1 ? min(pos[e], first_pos - 1) : pos[e];
         slope[e] = a.slopes ? a.slopes[kvh * group + R % group] * LOG2E : 0.f;
     }
-    const float scale2 = a.scale * LOG2E;
+    const float scale2 = a.scale * LOG2E, cap2 = a.softcap * LOG2E, cap_in = a.softcap > 0.f ? a.scale / a.softcap : 0.f;
     // the keys that every row of this warp sees: from the newest row's window start to the oldest row's position
     int warp_lo, warp_hi;
     {
         const int R0 = min(row0 + warp * 16, rows_total - 1), R1 = min(row0 + warp * 16 + 15, rows_total - 1);
         const int p0 = first_pos + R0 / group, p1 = first_pos + R1 / group;
         warp_lo = a.window > 0 ? max(0, p1 - a.window + 1) : 0;
+        if (a.chunk > 0) warp_lo = max(warp_lo, p1 - p1 % a.chunk);
         if (a.key_part == 2) warp_lo = max(warp_lo, first_pos);
         warp_hi = a.key_part == 1 ? min(p0, first_pos - 1) : p0;
     }
@@ -184,7 +193,7 @@ attention_rows_mma_kernel(const RowsArgs<bf16> a, int splits, float* __restrict_
         __syncthreads();
         const bf16* kt = Ks + stage * BN * kp;
         const bf16* vt = Vs + stage * v_stage;
-        const int j0 = j_first + t * BN;
+        const int j0 = tile_start(t);
 
         float s[BN / 8][4];
 #pragma unroll
@@ -204,16 +213,17 @@ attention_rows_mma_kernel(const RowsArgs<bf16> a, int splits, float* __restrict_
         // scale, bias, mask (scores in units of log 2 from here on); the tile's maximum per row
         // (maxima and sums are kept in two halves per row, joined at the end: half as long a chain of dependent operations)
         float part_max[2][2] = {{-INFINITY, -INFINITY}, {-INFINITY, -INFINITY}};
-        const bool whole = j0 >= warp_lo && j0 + BN - 1 <= warp_hi;  // every row of the warp sees every key of the tile
-        const bool biased = a.slopes != nullptr;
+        // every row of the warp sees every key of the tile: inside all windows, or among the kept first keys
+        const bool whole = (j0 >= warp_lo || j0 + BN <= kf) && j0 + BN - 1 <= warp_hi;
+        const bool biased = a.slopes != nullptr, capped = a.softcap > 0.f;
 #pragma unroll
         for (int nb = 0; nb < BN / 8; ++nb)
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 const int e = c >> 1, j = j0 + nb * 8 + (lane & 3) * 2 + (c & 1);
-                float v = s[nb][c] * scale2;
+                float v = capped ? cap2 * tanhf(s[nb][c] * cap_in) : s[nb][c] * scale2;
                 if (biased) v -= slope[e] * (float)(pos[e] - j);
-                if (!whole) v = (j >= lo[e] && j <= hi[e]) ? v : -INFINITY;
+                if (!whole) v = ((j >= lo[e] || j < kf) && j <= hi[e]) ? v : -INFINITY;
                 s[nb][c] = v;
                 part_max[e][nb & 1] = fmaxf(part_max[e][nb & 1], v);
             }
@@ -460,7 +470,7 @@ LLM_EXPORT int llm_attention_rows_mma(const void* q0, long long q0_token, long l
                                       int n_tokens, int requests, int max_query_len, int H, int KV, int page_size, int window,
                                       float scale, int splits, float* part_o, float* part_ml, int key_part, const void* keys1,
                                       long long k1_token, int fresh_d0, float* stats, const float* sinks, const float* gate,
-                                      long long gate_token, cudaStream_t stream) {
+                                      long long gate_token, int keep_first, int chunk, float softcap, cudaStream_t stream) {
     if (n_tokens <= 0 || requests <= 0) return 0;
     if (d0 <= 0 || d1 < 0 || dv <= 0 || H <= 0 || KV <= 0 || H % KV || page_size <= 0 || table_width <= 0 || splits < 1 ||
         max_query_len < 1 || (d1 > 0 && q1 == nullptr) || (splits > 1 && (part_o == nullptr || part_ml == nullptr)))
@@ -469,6 +479,7 @@ LLM_EXPORT int llm_attention_rows_mma(const void* q0, long long q0_token, long l
     auto aligned = [](const void* p) { return ((uintptr_t)p & 15) == 0; };
     if ((d0 & 15) || (d1 & 15) || (dv & 15) || dv > 256 || dk > 640) return LLM_ERR_UNSUPPORTED;
     if (key_part < 0 || key_part > 2 || (stats && splits != 1)) return LLM_ERR_BAD_ARGUMENT;
+    if (keep_first < 0 || chunk < 0 || (keep_first > 0 && key_part != 0)) return LLM_ERR_BAD_ARGUMENT;  // kept keys belong to a whole softmax
     if ((sinks || gate) && (key_part != 0 || stats)) return LLM_ERR_BAD_ARGUMENT;  // a sink belongs to a whole softmax, not to a part of one
     if (gate && (splits > 1 && out == nullptr)) return LLM_ERR_BAD_ARGUMENT;
     if (key_part == 2 && keys1 && ((fresh_d0 & 15) || fresh_d0 <= 0 || fresh_d0 >= dk || (k1_token & 7) || ((uintptr_t)keys1 & 15)))
@@ -488,7 +499,7 @@ LLM_EXPORT int llm_attention_rows_mma(const void* q0, long long q0_token, long l
     a.page_table = page_table; a.token_request = token_request; a.cu_tokens = cu_tokens; a.ctx_lens = ctx_lens;
     a.slopes = slopes;
     a.table_width = table_width; a.n_tokens = n_tokens; a.H = H; a.KV = KV; a.page_size = page_size; a.window = window;
-    a.scale = scale;
+    a.scale = scale; a.keep_first = keep_first; a.chunk = chunk; a.softcap = softcap;
     a.key_part = key_part; a.keys1 = key_part == 2 ? (const bf16*)keys1 : nullptr; a.k1_token = k1_token; a.fresh_d0 = fresh_d0;
     a.stats = stats;
     a.sinks = sinks; a.gate = gate; a.gate_token = gate_token;

@@ -7,6 +7,9 @@
 //   norm:      every query head and every key head is divided by sqrt(mean(x^2) + eps) over its D lanes and multiplied
 //              by qw / kw [D], the same for every head
 //   rotate:    lanes i and i + rot/2 (i < rot/2) of every head turn by position * freq[i]; lanes >= rot pass
+//              (interleaved: lanes 2i and 2i + 1 instead)
+//   values:    v_keep [N, Hk * V] (float32) takes the values as projected, bias included; or, with v_first [N, Hk * V],
+//              the values become (1 - v_lambda) v + v_lambda v_first (those of the same token in an earlier layer)
 //   warm:      queries times 1 + coef * ln(floor((position + 1) / every) + 1)
 // Queries go to q_out [N, Hq * D]; keys and values into the token's slot of pool [pages, 2, Hk, page_size, Dp].
 // Everything is computed in 32-bit.  One CTA per token, one warp per head at a time.
@@ -24,7 +27,8 @@ head_prepare_kernel(const TI* __restrict__ proj, int ldp, const float* __restric
                     TK* __restrict__ pool, const int* __restrict__ slot_map, int page_size, int Dp, const float* __restrict__ qw,
                     const float* __restrict__ kw, float eps, int normed, const float* __restrict__ freq, int rot,
                     const int* __restrict__ positions, float warm_coef, int warm_every, int Hq, int Hk, int D, int V,
-                    int values_are_keys) {
+                    int values_are_keys, int interleaved, float* __restrict__ v_keep, const float* __restrict__ v_first,
+                    float v_lambda) {
     extern __shared__ float smem[];  // [WARPS][D] a head as projected, then rot/2 (cos, sin) pairs
     float2* turn = reinterpret_cast<float2*>(smem + WARPS * D + ((WARPS * D) & 1));
     pdl_trigger();
@@ -65,7 +69,7 @@ head_prepare_kernel(const TI* __restrict__ proj, int ldp, const float* __restric
             float a, b = 0.f;
             int da, db = -1;
             if (i < half) {
-                da = i; db = i + half;
+                da = interleaved ? 2 * i : i; db = interleaved ? 2 * i + 1 : i + half;
                 float u = buf[da] * ns, v = buf[db] * ns;
                 if (w) { u *= w[da]; v *= w[db]; }
                 const float c = turn[i].x, s = turn[i].y;
@@ -95,6 +99,8 @@ head_prepare_kernel(const TI* __restrict__ proj, int ldp, const float* __restric
             const int kh = i / V, d = i % V;
             float v = to_float(row[vbase + i]);
             if (bias) v += bias[vbase + i];
+            if (v_keep) v_keep[(size_t)t * Hk * V + i] = v;
+            if (v_first) v = (1.f - v_lambda) * v + v_lambda * v_first[(size_t)t * Hk * V + i];
             pool[((((size_t)page * 2 + 1) * Hk + kh) * page_size + off) * Dp + d] = from_float<TK>(v);
         }
     }
@@ -106,18 +112,19 @@ head_prepare_kernel(const TI* __restrict__ proj, int ldp, const float* __restric
 LLM_EXPORT int llm_head_prepare(const void* proj, int in_dtype, int ldp, const float* bias, void* q_out, int ldq, void* pool,
                                 int out_dtype, const int* slot_map, int page_size, int Dp, const float* qw, const float* kw, float eps,
                                 int normed, const float* freq, int rot, const int* positions, float warm_coef, int warm_every, int N,
-                                int Hq, int Hk, int D, int V, int values_are_keys, cudaStream_t stream) {
+                                int Hq, int Hk, int D, int V, int values_are_keys, int interleaved, float* v_keep,
+                                const float* v_first, float v_lambda, cudaStream_t stream) {
     if (N <= 0) return 0;
     if (rot < 0 || rot % 2 || rot > D || Hq < 0 || Hk < 0 || D <= 0 || D > 1024 || (Hk > 0 && (!pool || !slot_map || Dp < D || page_size <= 0)) ||
         (Hk > 0 && !values_are_keys && (V <= 0 || Dp < V)) || ((rot > 0 || warm_every > 0) && !positions) || (rot > 0 && !freq) ||
-        (normed && (!qw || (Hk > 0 && !kw))) || (Hq > 0 && !q_out))
+        (normed && (!qw || (Hk > 0 && !kw))) || (Hq > 0 && !q_out) || ((v_keep || v_first) && (values_are_keys || Hk <= 0)))
         return LLM_ERR_BAD_ARGUMENT;
     using bf = __nv_bfloat16;
     const size_t smem = ((size_t)WARPS * D + 1) * sizeof(float) + (size_t)(rot / 2 + 1) * sizeof(float2);
     auto go = [&](auto kernel, auto* in, auto* qo) {
         using TK = std::remove_pointer_t<decltype(qo)>;
         return launch_pdl(kernel, dim3(N), dim3(WARPS * 32), smem, stream, in, ldp, bias, qo, ldq, (TK*)pool, slot_map, page_size, Dp, qw, kw,
-                          eps, normed, freq, rot, positions, warm_coef, warm_every, Hq, Hk, D, V, values_are_keys);
+                          eps, normed, freq, rot, positions, warm_coef, warm_every, Hq, Hk, D, V, values_are_keys, interleaved, v_keep, v_first, v_lambda);
     };
     if (in_dtype == LLM_F32 && out_dtype == LLM_F32) return go(head_prepare_kernel<float, float, float>, (const float*)proj, (float*)q_out);
     if (in_dtype == LLM_F32 && out_dtype == LLM_BF16) return go(head_prepare_kernel<float, bf, bf>, (const float*)proj, (bf*)q_out);

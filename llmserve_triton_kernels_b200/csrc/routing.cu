@@ -15,14 +15,15 @@ namespace {
 //   w[t, E] = sigmoid(z[t, E]) if shared_gate
 // w: [N, E + shared_gate] float32
 // One warp: from a token's logits zr[0 : E (+ 1)] to its row of weights wr; s, c: E floats of scratch each.
+// bias (or null): added to the logits of the E experts first.  shared_gate 2: w[t, E] = 1 (a shared expert without a gate; z has no column E).
 __device__ __forceinline__ void route_row(const float* zr, const float* __restrict__ correction, float* wr, float* s, float* c, int E, int top,
-                                          float scale, int renorm, int shared_gate, int lane) {
+                                          float scale, int renorm, int shared_gate, int lane, const float* __restrict__ bias = nullptr) {
     float m = -FLT_MAX;
-    for (int e = lane; e < E; e += 32) m = fmaxf(m, zr[e]);
+    for (int e = lane; e < E; e += 32) m = fmaxf(m, zr[e] + (bias ? bias[e] : 0.f));
     m = warp_max(m);
     float sum = 0.f;
     for (int e = lane; e < E; e += 32) {
-        const float x = expf(zr[e] - m);
+        const float x = expf(zr[e] + (bias ? bias[e] : 0.f) - m);
         s[e] = x;
         sum += x;
     }
@@ -58,7 +59,7 @@ __device__ __forceinline__ void route_row(const float* zr, const float* __restri
     const float f = renorm ? scale / chosen_sum : scale;
     for (int e = lane; e < E; e += 32)
         if (wr[e] < 0.f) wr[e] = s[e] * f;
-    if (shared_gate && lane == 0) wr[E] = 1.f / (1.f + expf(-zr[E]));
+    if (shared_gate && lane == 0) wr[E] = shared_gate == 2 ? 1.f : 1.f / (1.f + expf(-zr[E]));
 }
 
 __global__ void __launch_bounds__(128)
@@ -81,11 +82,11 @@ route_topk_kernel(const float* __restrict__ z, int ldz, const float* __restrict_
 template <typename TX, int TT>
 __global__ void __launch_bounds__(512)
 router_kernel(const TX* __restrict__ x, int ldx, const float* __restrict__ wr, const float* __restrict__ correction, float* __restrict__ out,
-              int N, int K, int E, int top, float scale, int renorm, int shared_gate) {
+              int N, int K, int E, int top, float scale, int renorm, int shared_gate, const float* __restrict__ bias) {
     constexpr int RPW = 4;  // rows of the router matrix a warp sums up at once: what it reads of the tokens serves all four
     extern __shared__ float sm[];  // z[TT][rows], then per token s[E], c[E]
     pdl_trigger();
-    const int rows = E + shared_gate, t0 = blockIdx.x * TT;
+    const int rows = E + (shared_gate == 1), out_w = E + (shared_gate != 0), t0 = blockIdx.x * TT;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
     float* z = sm;
     pdl_wait();
@@ -147,7 +148,7 @@ router_kernel(const TX* __restrict__ x, int ldx, const float* __restrict__ wr, c
     __syncthreads();
     if (warp < TT && t0 + warp < N) {
         float* s = sm + (size_t)TT * rows + (size_t)warp * 2 * E;
-        route_row(z + warp * rows, correction, out + (size_t)(t0 + warp) * rows, s, s + E, E, top, scale, renorm, shared_gate, lane);
+        route_row(z + warp * rows, correction, out + (size_t)(t0 + warp) * out_w, s, s + E, E, top, scale, renorm, shared_gate, lane, bias);
     }
 }
 
@@ -208,7 +209,7 @@ template <typename T, int RUN>
 __global__ void __launch_bounds__(256)
 expert_gated_act_kernel(const T* __restrict__ x, int ldx, T* __restrict__ y, int ldy, const float* __restrict__ w, int ldw,
                         const int* __restrict__ ids, const int* __restrict__ table, int top, int vocab, int E, int ff, int fs,
-                        float limit, float limit_s, float slope) {
+                        float limit, float limit_s, float slope, float up_shift) {
     pdl_trigger();
     const int t = blockIdx.y;
     const int C = E * ff + fs;
@@ -251,7 +252,7 @@ expert_gated_act_kernel(const T* __restrict__ x, int ldx, T* __restrict__ y, int
 #pragma unroll
             for (int c = 0; c < RUN; ++c) {
                 const float gc = fminf(g[c], lim), uc = fminf(fmaxf(u[c], -lim), lim);
-                out[c] = gc / (1.f + expf(-slope * gc)) * (uc + 1.f) * wt;
+                out[c] = gc / (1.f + expf(-slope * gc)) * (uc + up_shift) * wt;
             }
         }
         T* dst = y + (size_t)t * ldy + j;
@@ -379,12 +380,12 @@ LLM_EXPORT int llm_route_topk(const float* z, int ldz, const float* correction, 
 }
 
 LLM_EXPORT int llm_router(const void* x, int x_dtype, int ldx, const float* wr, const float* correction, float* out, int N, int K, int E,
-                          int top, float scale, int renorm, int shared_gate, cudaStream_t stream) {
+                          int top, float scale, int renorm, int shared_gate, const float* bias, cudaStream_t stream) {
     if (N <= 0) return 0;
-    if (E <= 0 || top < 1 || top > E || E > 2048 || K <= 0) return LLM_ERR_BAD_ARGUMENT;
+    if (E <= 0 || top < 1 || top > E || E > 2048 || K <= 0 || shared_gate < 0 || shared_gate > 2) return LLM_ERR_BAD_ARGUMENT;
     // tokens a CTA: one for steps of few tokens (more CTAs, more loads in flight a warp), two otherwise (three CTAs an SM)
     const int TT = N <= 32 ? 1 : 2;
-    const int rows_all = E + (shared_gate ? 1 : 0);
+    const int rows_all = E + (shared_gate == 1 ? 1 : 0);  // rows of the router's matrix (2: the last column of out is the constant 1)
     const size_t smem = ((size_t)TT * rows_all + (size_t)TT * 2 * E) * sizeof(float);
     const int groups = (rows_all + 3) / 4;  // of four rows: a warp each, as far as 16 warps go
     const dim3 grid((N + TT - 1) / TT), block(32 * (groups < 4 ? 4 : groups > 16 ? 16 : groups));
@@ -393,7 +394,7 @@ LLM_EXPORT int llm_router(const void* x, int x_dtype, int ldx, const float* wr, 
             const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             if (e != cudaSuccess) return (int)e;
         }
-        return launch_pdl(kernel, grid, block, smem, stream, xp, ldx, wr, correction, out, N, K, E, top, scale, renorm, shared_gate ? 1 : 0);
+        return launch_pdl(kernel, grid, block, smem, stream, xp, ldx, wr, correction, out, N, K, E, top, scale, renorm, shared_gate, bias);
     };
     using bf = __nv_bfloat16;
     if (x_dtype == LLM_F32) return TT == 1 ? go(router_kernel<float, 1>, (const float*)x) : go(router_kernel<float, 2>, (const float*)x);
@@ -422,7 +423,7 @@ LLM_EXPORT int llm_expert_act_scale(const void* x, int ldx, const float* w, int 
 
 LLM_EXPORT int llm_expert_gated_act(const void* x, int ldx, void* y, int ldy, int dtype, const float* w, int ldw, const int* ids,
                                     const int* table, int top, int vocab, int N, int E, int ff, int fs, float limit, float limit_s,
-                                    float slope, cudaStream_t stream) {
+                                    float slope, float up_shift, cudaStream_t stream) {
     const int C = E * ff + fs;
     if (N <= 0 || C <= 0) return 0;
     if (E < 0 || ff < 0 || fs < 0 || N > 65535 || (!w && (!ids || !table || top < 0 || vocab <= 0))) return LLM_ERR_BAD_ARGUMENT;
@@ -432,7 +433,7 @@ LLM_EXPORT int llm_expert_gated_act(const void* x, int ldx, void* y, int ldy, in
     const dim3 grid(blocks < 64 ? blocks : 64, N), block(256);
     using bf = __nv_bfloat16;
     auto go = [&](auto kernel, auto* xp, auto* yp) {
-        return launch_pdl(kernel, grid, block, 0, stream, xp, ldx, yp, ldy, w, ldw, ids, table, top, vocab, E, ff, fs, limit, limit_s, slope);
+        return launch_pdl(kernel, grid, block, 0, stream, xp, ldx, yp, ldy, w, ldw, ids, table, top, vocab, E, ff, fs, limit, limit_s, slope, up_shift);
     };
     if (dtype == LLM_F32)
         return wide ? go(expert_gated_act_kernel<float, 4>, (const float*)x, (float*)y) : go(expert_gated_act_kernel<float, 1>, (const float*)x, (float*)y);

@@ -1,0 +1,97 @@
+// A short causal convolution over time on every channel of a token's projections, across the steps of a request.
+//
+//   y[t, c] = sum_j w[c, j] * u[t - (taps - 1) + j, c]        j = 0 .. taps - 1,  zeros before the request's first token
+//
+// u are the rows of a flat batch (request r owns rows cu[r] .. cu[r + 1] - 1); what lies before a request's first row of
+// this step comes from its slot of `state` [slots, taps - 1, C] (float32): the last taps - 1 rows of u that earlier steps
+// brought, oldest first (zeros where the request has had fewer).  A second kernel, which starts when every read of the
+// first has been made, moves the slot on to the last taps - 1 rows after this step.  Sums are 32-bit, in the order of j.
+#include "common.cuh"
+
+namespace {
+
+constexpr int MAX_TAPS = 16;
+
+// grid (channel blocks, token tiles); a thread a channel, TOKENS rows a CTA
+template <typename TI, int TOKENS>
+__global__ void __launch_bounds__(128)
+short_conv_kernel(const TI* __restrict__ u, int ldu, const float* __restrict__ w, const float* __restrict__ state,
+                  const int* __restrict__ state_slots, const int* __restrict__ token_request, const int* __restrict__ cu_tokens,
+                  float* __restrict__ y, int ldy, int N, int C, int taps) {
+    pdl_trigger();
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    float wt[MAX_TAPS];
+    if (c < C)
+#pragma unroll
+        for (int j = 0; j < MAX_TAPS; ++j) wt[j] = j < taps ? w[(size_t)c * taps + j] : 0.f;
+    pdl_wait();
+    if (c >= C) return;
+    const int t0 = blockIdx.y * TOKENS, back = taps - 1;
+    for (int t = t0; t < min(N, t0 + TOKENS); ++t) {
+        const int r = token_request[t], begin = cu_tokens[r];
+        const float* old = state + (size_t)state_slots[r] * back * C;
+        float acc = 0.f;
+#pragma unroll
+        for (int j = 0; j < MAX_TAPS; ++j) {
+            if (j >= taps) break;
+            const int src = t - back + j;  // a row of this step, or (before the request's first) of its slot
+            const float v = src >= begin ? to_float(u[(size_t)src * ldu + c]) : old[(size_t)(src - begin + back) * C + c];
+            acc = fmaf(wt[j], v, acc);
+        }
+        y[(size_t)t * ldy + c] = acc;
+    }
+}
+
+// grid (channel blocks, requests): the slot's rows after this step are the last taps - 1 of (old rows, this step's rows)
+template <typename TI>
+__global__ void __launch_bounds__(128)
+short_conv_state_kernel(const TI* __restrict__ u, int ldu, float* __restrict__ state, const int* __restrict__ state_slots,
+                        const int* __restrict__ cu_tokens, int C, int taps) {
+    pdl_trigger();
+    pdl_wait();
+    const int c = blockIdx.x * blockDim.x + threadIdx.x, r = blockIdx.y;
+    if (c >= C) return;
+    const int begin = cu_tokens[r], count = cu_tokens[r + 1] - begin, back = taps - 1;
+    float* slot = state + (size_t)state_slots[r] * back * C;
+    float next[MAX_TAPS];
+#pragma unroll
+    for (int s = 0; s < MAX_TAPS; ++s) {
+        if (s >= back) break;
+        const int src = count + s - back;  // counted from the request's first row of this step
+        next[s] = src >= 0 ? to_float(u[(size_t)(begin + src) * ldu + c]) : slot[(size_t)(count + s) * C + c];
+    }
+#pragma unroll
+    for (int s = 0; s < MAX_TAPS; ++s) {
+        if (s >= back) break;
+        slot[(size_t)s * C + c] = next[s];
+    }
+}
+
+}  // namespace
+
+// u [N, >= C] (float32 or bfloat16, row pitch ldu), w [C, taps] float32, state [slots, taps - 1, C] float32,
+// y [N, C] float32 (row pitch ldy).  taps from 1 to 16 (1: a weight a channel, no state).
+LLM_EXPORT int llm_short_conv(const void* u, int dtype, int ldu, const float* w, float* state, const int* state_slots,
+                              const int* token_request, const int* cu_tokens, float* y, int ldy, int N, int requests, int C,
+                              int taps, cudaStream_t stream) {
+    if (N <= 0 || requests <= 0) return 0;
+    if (C <= 0 || taps < 1 || taps > MAX_TAPS || ldu < C || ldy < C || (taps > 1 && !state) || requests > 65535) return LLM_ERR_BAD_ARGUMENT;
+    constexpr int TOKENS = 8;
+    const dim3 block(128), grid((C + 127) / 128, (N + TOKENS - 1) / TOKENS);
+    if (grid.y > 65535) return LLM_ERR_UNSUPPORTED;
+    int code;
+    if (dtype == LLM_F32)
+        code = launch_pdl(short_conv_kernel<float, TOKENS>, grid, block, 0, stream, (const float*)u, ldu, w, (const float*)state, state_slots,
+                          token_request, cu_tokens, y, ldy, N, C, taps);
+    else if (dtype == LLM_BF16)
+        code = launch_pdl(short_conv_kernel<__nv_bfloat16, TOKENS>, grid, block, 0, stream, (const __nv_bfloat16*)u, ldu, w,
+                          (const float*)state, state_slots, token_request, cu_tokens, y, ldy, N, C, taps);
+    else
+        return LLM_ERR_BAD_ARGUMENT;
+    if (code != 0 || taps == 1) return code;
+    const dim3 sgrid((C + 127) / 128, requests);
+    if (dtype == LLM_F32)
+        return launch_pdl(short_conv_state_kernel<float>, sgrid, block, 0, stream, (const float*)u, ldu, state, state_slots, cu_tokens, C, taps);
+    return launch_pdl(short_conv_state_kernel<__nv_bfloat16>, sgrid, block, 0, stream, (const __nv_bfloat16*)u, ldu, state, state_slots,
+                      cu_tokens, C, taps);
+}

@@ -226,10 +226,32 @@ __global__ void gate_mul_kernel(const T* __restrict__ a, long long a_token_strid
         const int c = (int)(i - t * cols);
         const int h = c / head_width, j = c - h * head_width;
         const float av = to_float(a[(long long)t * a_token_stride + (long long)h * a_head_stride + j]);
-        const float bv = to_float(b[t * ldb + c]);
-        const float gate = kind == 0 ? sigmoid_f(bv) : bv * sigmoid_f(bv);
+        const float bv = to_float(b[t * ldb + ((kind & 2) ? h : c)]);  // kind & 2: one gate a head, b [N, heads]
+        const float gate = (kind & 1) == 0 ? sigmoid_f(bv) : bv * sigmoid_f(bv);
         out[t * ldo + c] = from_float<T>(av * gate);
     }
+}
+
+// out[t, :] = x[t, :cols] / sqrt(mean(x[t, :cols]^2) + eps) * weight: the RMS norm of a run of columns of rows that have
+// a pitch (a part of a stacked projection), statistics in 32-bit; a warp a row.
+template <typename TI, typename TO>
+__global__ void __launch_bounds__(128)
+row_rmsnorm_kernel(const TI* __restrict__ x, int ldx, const float* __restrict__ weight, float eps, TO* __restrict__ out, int ldo,
+                   int rows, int cols) {
+    pdl_trigger();
+    pdl_wait();
+    const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (row >= rows) return;
+    const TI* src = x + (size_t)row * ldx;
+    float ss = 0.f;
+    for (int i = lane; i < cols; i += 32) {
+        const float v = to_float(src[i]);
+        ss = fmaf(v, v, ss);
+    }
+    ss = warp_sum(ss);
+    const float scale = 1.f / sqrtf(ss / (float)cols + eps);
+    TO* dst = out + (size_t)row * ldo;
+    for (int i = lane; i < cols; i += 32) dst[i] = from_float<TO>(to_float(src[i]) * scale * weight[i]);
 }
 
 int flat_blocks(size_t total, int threads) {
@@ -294,7 +316,8 @@ LLM_EXPORT int llm_unary(const void* x, int ldx, void* out, int ldo, int dtype, 
 LLM_EXPORT int llm_gate_mul(const void* a, long long a_token_stride, long long a_head_stride, int head_width, const void* b,
                             int ldb, void* out, int ldo, int dtype, int rows, int cols, int kind, cudaStream_t stream) {
     if (rows <= 0 || cols <= 0) return 0;
-    if (head_width <= 0 || cols % head_width || ldb < cols || ldo < cols || kind < 0 || kind > 1) return LLM_ERR_BAD_ARGUMENT;
+    if (head_width <= 0 || cols % head_width || ldb < ((kind & 2) ? cols / head_width : cols) || ldo < cols || kind < 0 || kind > 3)
+        return LLM_ERR_BAD_ARGUMENT;
     const size_t total = (size_t)rows * cols;
     const int threads = 256, blocks = flat_blocks(total, threads);
     if (dtype == LLM_F32)
@@ -304,5 +327,23 @@ LLM_EXPORT int llm_gate_mul(const void* a, long long a_token_stride, long long a
         return launch_pdl(gate_mul_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, (const __nv_bfloat16*)a,
                           a_token_stride, a_head_stride, head_width, (const __nv_bfloat16*)b, ldb, (__nv_bfloat16*)out, ldo,
                           cols, total, kind);
+    return LLM_ERR_BAD_ARGUMENT;
+}
+
+// x [rows, >= cols] with row pitch ldx (float32 or bfloat16) -> out [rows, cols] with pitch ldo, of type out_dtype.
+LLM_EXPORT int llm_row_rmsnorm(const void* x, int x_dtype, int ldx, const float* weight, float eps, void* out, int out_dtype, int ldo,
+                               int rows, int cols, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (cols <= 0 || ldx < cols || ldo < cols || !weight) return LLM_ERR_BAD_ARGUMENT;
+    using bf = __nv_bfloat16;
+    const dim3 grid((rows + 3) / 4), block(128);
+    if (x_dtype == LLM_F32 && out_dtype == LLM_F32)
+        return launch_pdl(row_rmsnorm_kernel<float, float>, grid, block, 0, stream, (const float*)x, ldx, weight, eps, (float*)out, ldo, rows, cols);
+    if (x_dtype == LLM_F32 && out_dtype == LLM_BF16)
+        return launch_pdl(row_rmsnorm_kernel<float, bf>, grid, block, 0, stream, (const float*)x, ldx, weight, eps, (bf*)out, ldo, rows, cols);
+    if (x_dtype == LLM_BF16 && out_dtype == LLM_BF16)
+        return launch_pdl(row_rmsnorm_kernel<bf, bf>, grid, block, 0, stream, (const bf*)x, ldx, weight, eps, (bf*)out, ldo, rows, cols);
+    if (x_dtype == LLM_BF16 && out_dtype == LLM_F32)
+        return launch_pdl(row_rmsnorm_kernel<bf, float>, grid, block, 0, stream, (const bf*)x, ldx, weight, eps, (float*)out, ldo, rows, cols);
     return LLM_ERR_BAD_ARGUMENT;
 }

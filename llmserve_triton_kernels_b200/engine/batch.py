@@ -50,6 +50,9 @@ class StepContext:
     # them before the step, which a mixer may use to leave out the work over cached rows.  A graph is captured for one
     # value of this and replayed only for steps of the same kind.
     fresh_requests: bool = False
+    # what the parts of one pass hand to one another across layers (a tensor of this step's tokens that a later layer
+    # reads, by a key the two agree on); emptied when a pass starts
+    shared: dict = field(default_factory=dict)
 
 
 def pack_step(entries: list[StepEntry], lengths: list[int], state_slots: np.ndarray, group_arrays, device):

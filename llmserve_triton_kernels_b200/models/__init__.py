@@ -2,4 +2,4 @@
 
 from .plan import Injection, LayerRun, LayerSpec, ModelPlan  # noqa: F401
 from .model import Model  # noqa: F401
-from . import kafepel, llama, nudodra, nurolorn  # noqa: F401,E402
+from . import kafepel, llama, nudodra, nurolorn, tenotar  # noqa: F401,E402

@@ -124,6 +124,9 @@ class Model:
         of entry i's cache.  Returns 32-bit logits ``[len(ctx.logit_rows), vocab]``."""
         if ops.checked():
             self._check_step(ctx, caches)
+        shared = getattr(ctx, "shared", None)
+        if shared is not None:
+            shared.clear()  # nothing of an earlier pass over this context is handed on
         resid = self.embed_tokens(ctx)
         pending = None
         order = self.plan.schedule

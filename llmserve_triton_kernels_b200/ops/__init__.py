@@ -47,14 +47,14 @@ _SIGNATURES = {
     "llm_unary": [_vp, _i, _vp, _i, _i, _i, _i, _i, _f, _vp],
     "llm_gate_mul": [_vp, _ll, _ll, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _vp],
     "llm_mingru_scan": [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
-    "llm_latent_prepare": [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _f, _i, _i, _i, _i, _i, _i, _vp],
+    "llm_latent_prepare": [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _f, _i, _i, _i, _i, _i, _i, _vp, _i, _i, _i, _vp],
     "llm_merge_project_gate": [_vp, _vp, _i, _vp, _vp, _i, _vp, _i, _i, _i, _i, _vp],
     "llm_merge_two_parts": [_vp, _ll, _ll, _vp, _vp, _ll, _ll, _vp, _vp, _ll, _ll, _i, _i, _i, _vp],
     "llm_unit_norm_kv_write": [_vp, _i, _i, _vp, _vp, _f, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
     "llm_attention_rows": [_vp, _ll, _ll, _i, _vp, _ll, _ll, _i, _vp, _ll, _ll, _vp, _ll, _ll, _ll, _vp, _ll, _ll, _ll, _i, _i,
-                           _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _vp, _vp, _ll, _vp],
+                           _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _vp, _vp, _ll, _i, _i, _f, _vp],
     "llm_attention_rows_mma": [_vp, _ll, _ll, _i, _vp, _ll, _ll, _i, _vp, _ll, _ll, _vp, _ll, _ll, _ll, _vp, _ll, _ll, _ll, _i,
-                               _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _vp, _vp, _i, _vp, _ll, _i, _vp, _vp, _vp, _ll, _vp],
+                               _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _vp, _vp, _i, _vp, _ll, _i, _vp, _vp, _vp, _ll, _i, _i, _f, _vp],
     "llm_gemm_simt_batched": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _ll, _ll, _ll, _vp],
     "llm_sample": [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
     "llm_sigmoid_attention": [_vp, _i, _i, _vp, _i, _vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _f, _i,
@@ -66,10 +66,12 @@ _SIGNATURES = {
     "llm_head_norm_gate": [_vp, _vp, _i, _i, _vp, _i, _i, _i, _i, _f, _i, _vp, _vp],
     "llm_embed_copies": [_vp, _vp, _i, _vp, _i, _i, _i, _i, _vp],
     "llm_hyper_mix_norm": [_vp, _vp, _vp, _vp, _vp, _f, _f, _f, _f, _i, _vp, _vp, _vp, _vp, _f, _vp, _vp, _i, _i, _i, _i, _i, _vp],
-    "llm_head_prepare": [_vp, _i, _i, _vp, _vp, _i, _vp, _i, _vp, _i, _i, _vp, _vp, _f, _i, _vp, _i, _vp, _f, _i, _i, _i, _i, _i, _i, _i, _vp],
+    "llm_head_prepare": [_vp, _i, _i, _vp, _vp, _i, _vp, _i, _vp, _i, _i, _vp, _vp, _f, _i, _vp, _i, _vp, _f, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _f, _vp],
+    "llm_short_conv": [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
+    "llm_row_rmsnorm": [_vp, _i, _i, _vp, _f, _vp, _i, _i, _i, _i, _vp],
     "llm_gated_scan": [_vp, _i, _vp, _i, _vp, _i, _i, _vp, _i, _vp, _f, _f, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _i, _vp],
-    "llm_expert_gated_act": [_vp, _i, _vp, _i, _i, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _f, _f, _vp],
-    "llm_router": [_vp, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _i, _vp],
+    "llm_expert_gated_act": [_vp, _i, _vp, _i, _i, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _f, _f, _f, _vp],
+    "llm_router": [_vp, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _i, _vp, _vp],
     "llm_route_topk": [_vp, _i, _vp, _vp, _i, _i, _i, _f, _i, _i, _vp],
     "llm_expert_act_scale": [_vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
     "llm_branch_sum_norm": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _f, _f, _f, _vp],
@@ -959,16 +961,16 @@ def linear_act(x, w: torch.Tensor, activation: str) -> torch.Tensor:
     return unary(linear(x, w), activation, inplace=True)
 
 
-def gate_mul(a: torch.Tensor, b: torch.Tensor, kind: str = "sigmoid") -> torch.Tensor:
+def gate_mul(a: torch.Tensor, b: torch.Tensor, kind: str = "sigmoid", per_head: bool = False) -> torch.Tensor:
     """``a [N, heads, W]`` (any token and head strides) times ``gate(b [N, heads * W])`` -> ``[N, heads * W]``;
-    the gate (``sigmoid`` or ``silu``) and the product are 32-bit."""
+    the gate (``sigmoid`` or ``silu``) and the product are 32-bit.  ``per_head``: one gate a head, ``b [N, heads]``."""
     _need(kind in _GATE_KINDS, f"no gate {kind!r}; known: {sorted(_GATE_KINDS)}")
     _need(a.dim() == 3 and a.stride(2) == 1 and b.dim() == 2 and b.stride(1) == 1 and a.dtype == b.dtype, "gate_mul: a [N, heads, W], b [N, heads * W]")
     n, heads, w = a.shape
-    _need(b.shape[0] == n and b.shape[1] == heads * w, "gate_mul: the gate does not match the heads")
+    _need(b.shape[0] == n and b.shape[1] == (heads if per_head else heads * w), "gate_mul: the gate does not match the heads")
     out = torch.empty((n, heads * w), dtype=a.dtype, device=a.device)
     code = _launch("llm_gate_mul", _ptr(a), a.stride(0), a.stride(1), w, _ptr(b), b.stride(0), _ptr(out), heads * w,
-                   _code(a.dtype), n, heads * w, _GATE_KINDS[kind], _stream())
+                   _code(a.dtype), n, heads * w, _GATE_KINDS[kind] | (2 if per_head else 0), _stream())
     _check(code, "gate_mul")
     return out
 
@@ -994,13 +996,22 @@ def mingru_scan(proj: torch.Tensor, bias_z, bias_u, states: torch.Tensor, state_
 
 
 def latent_prepare(proj: torch.Tensor, positions: torch.Tensor, slot_map: torch.Tensor, plane: torch.Tensor, weight: torch.Tensor,
-                   freq: torch.Tensor, eps: float, heads: int, dim: int, rot: int, rank: int, fresh: bool = False):
+                   freq: torch.Tensor, eps: float, heads: int, dim: int, rot: int, rank: int, fresh: bool = False,
+                   queries: torch.Tensor | None = None, kv_col: int = 0, halves: bool = False):
     """For latent attention, from a token's stacked projections ``proj`` = ``[heads x (dim | rot) | rank | rot | ...]``:
     the queries' rotated parts (interleaved pairs, angles ``position * freq[i]`` in 32-bit) are returned as
     ``[N, heads, rot]``; the latent, RMS-normed with ``weight``, and the rotated shared key part are written to the
     token's slot of ``plane [pages, page_size, rank + rot]``.  With ``fresh`` the written rows are also returned token by
-    token, ``[N, rank + rot]``: the result is then the pair ``(rotated query parts, rows)``."""
-    _need(proj.dim() == 2 and proj.stride(1) == 1 and proj.shape[1] >= heads * (dim + rot) + rank + rot, "latent_prepare: proj rows are too short")
+    token, ``[N, rank + rot]``: the result is then the pair ``(rotated query parts, rows)``.  ``queries``
+    (``[N, heads x (dim | rot)]``, rows may have a pitch): the queries lie there and ``proj`` holds ``[rank | rot]`` from
+    column ``kv_col`` on (queries that come through a latent of their own are a later product than the keys' latent).
+    ``halves``: the rotated lanes pair as ``(i, i + rot_dims / 2)`` instead of ``(2i, 2i + 1)``."""
+    if queries is None:
+        _need(proj.dim() == 2 and proj.stride(1) == 1 and proj.shape[1] >= heads * (dim + rot) + rank + rot, "latent_prepare: proj rows are too short")
+    else:
+        _need(proj.dim() == 2 and proj.stride(1) == 1 and proj.shape[1] >= kv_col + rank + rot, "latent_prepare: proj rows are too short")
+        _need(queries.dim() == 2 and queries.stride(1) == 1 and queries.dtype == proj.dtype and queries.shape[0] == proj.shape[0]
+              and queries.shape[1] >= heads * (dim + rot), "latent_prepare: the queries' rows are too short, or of another type")
     _need(plane.dtype == proj.dtype and plane.is_contiguous() and plane.dim() == 3 and plane.shape[2] == rank + rot, "latent_prepare: the plane must be [pages, page_size, rank + rot] of the rows' type")
     _need(weight.dtype == torch.float32 and weight.numel() == rank and freq.dtype == torch.float32 and freq.is_contiguous(), "latent_prepare: weight [rank] and freq are float32")
     _i32(positions, "positions")
@@ -1010,7 +1021,7 @@ def latent_prepare(proj: torch.Tensor, positions: torch.Tensor, slot_map: torch.
     rows = torch.empty((proj.shape[0], rank + rot), dtype=proj.dtype, device=proj.device) if fresh else None
     code = _launch("llm_latent_prepare", _ptr(proj), _code(proj.dtype), proj.stride(0), _ptr(q_rot), _ptr(rows), _ptr(positions),
                    _ptr(slot_map), _ptr(plane), _ptr(weight), _ptr(freq), float(eps), proj.shape[0], heads, dim, rot, rank, rot_dims,
-                   _stream())
+                   _ptr(queries), 0 if queries is None else queries.stride(0), int(kv_col), int(halves), _stream())
     _check(code, "latent_prepare")
     return (q_rot, rows) if fresh else q_rot
 
@@ -1051,7 +1062,8 @@ def head_linear(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
 def attention_rows(q0, q1, keys, k_strides, values, v_strides, value_dim: int, page_table, page_size: int, ctx, *, num_heads: int,
                    num_kv_heads: int, scale: float, window: int | None = None, slopes: torch.Tensor | None = None,
                    key_part: int = 0, keys1: int | None = None, k1_token: int = 0, fresh_d0: int = 0, want_stats: bool = False,
-                   leave_parts: bool = False, sinks: torch.Tensor | None = None, gate: torch.Tensor | None = None):
+                   leave_parts: bool = False, sinks: torch.Tensor | None = None, gate: torch.Tensor | None = None,
+                   keep_first: int | None = None, chunk: int | None = None, softcap: float | None = None):
     """Attention in its general form: queries ``q0 [N, H, d0]`` and optionally ``q1 [N, H, d1]`` (lanes behind q0's),
     keys and values addressed by ``(page, head, token)`` strides in elements, an optional bias ``-slopes[h] * distance``.
     Returns ``[N, H, value_dim]``.
@@ -1063,8 +1075,13 @@ def attention_rows(q0, q1, keys, k_strides, values, v_strides, value_dim: int, p
     ``leave_parts``: where the keys are cut over several CTAs the partial results are not merged but returned as an
     :class:`AttentionParts`, for a kernel that merges them on its way (:func:`merge_project_gate`).
     ``sinks`` (float32 ``[H]``): every head's softmax has one more term ``exp(sinks[h])`` in its denominator, with no key and
-    no value.  ``gate`` (float32 ``[N, >= H * value_dim]``, rows may have a pitch): the output is multiplied by its sigmoid."""
+    no value.  ``gate`` (float32 ``[N, >= H * value_dim]``, rows may have a pitch): the output is multiplied by its sigmoid.
+    ``keep_first``: with a window, the keys at positions below it stay visible to every later query.  ``chunk``: a query sees
+    only the keys of its own block of so many positions, counted from 0.  ``softcap``: a scaled score s becomes
+    ``softcap * tanh(s / softcap)`` before the distance bias is taken off."""
     n, d0 = q0.shape[0], q0.shape[2]
+    keep_first, chunk, softcap = int(keep_first or 0) if window else 0, int(chunk or 0), float(softcap or 0.0)
+    _need(keep_first >= 0 and chunk >= 0 and softcap >= 0.0, "attention_rows: keep_first, chunk and softcap are not negative")
     if sinks is not None:
         _need(sinks.dtype == torch.float32 and sinks.numel() == num_heads and sinks.is_contiguous(), "sinks must be float32 [heads]")
     if gate is not None:
@@ -1082,7 +1099,9 @@ def attention_rows(q0, q1, keys, k_strides, values, v_strides, value_dim: int, p
         group = num_heads // num_kv_heads
         longest = getattr(ctx, "max_context_len", None) or int(ctx.context_lens.max())
         if window:
-            longest = min(longest, window + ctx.max_query_len)
+            longest = min(longest, window + keep_first + ctx.max_query_len)
+        if chunk:
+            longest = min(longest, chunk + ctx.max_query_len)
         ctas = -(-ctx.max_query_len * group // 64) * num_kv_heads * ctx.num_requests
         splits = max(1, min(-(-longest // 256), _sm_count() // ctas, 16, _SPLIT_SCRATCH_BYTES // (n * num_heads * value_dim * 4)))
         if key_part or want_stats:
@@ -1099,7 +1118,7 @@ def attention_rows(q0, q1, keys, k_strides, values, v_strides, value_dim: int, p
             value_dim, _ptr(page_table), page_table.shape[1], _ptr(ctx.token_request), _ptr(ctx.cu_tokens), _ptr(ctx.context_lens),
             _ptr(slopes), n, ctx.num_requests, ctx.max_query_len, num_heads, num_kv_heads, page_size, int(window or 0), float(scale),
             splits, _ptr(part_o), _ptr(part_ml), int(key_part), keys1, int(k1_token), int(fresh_d0), _ptr(stats), _ptr(sinks), _ptr(gate),
-            gate_token, _stream(),
+            gate_token, keep_first, chunk, softcap, _stream(),
         )
         if code != 10002:
             _check(code, "attention_rows (tensor cores)")
@@ -1114,7 +1133,7 @@ def attention_rows(q0, q1, keys, k_strides, values, v_strides, value_dim: int, p
         0 if q1 is None else q1.stride(1), d1, _ptr(out), out.stride(0), out.stride(1), keys, *k_strides, values, *v_strides,
         value_dim, _code(q0.dtype), _ptr(page_table), page_table.shape[1], _ptr(ctx.token_request), _ptr(ctx.cu_tokens),
         _ptr(ctx.context_lens), _ptr(slopes), n, num_heads, num_kv_heads, page_size, int(window or 0), float(scale), _ptr(sinks),
-        _ptr(gate), gate_token, _stream(),
+        _ptr(gate), gate_token, keep_first, chunk, softcap, _stream(),
     )
     _check(code, "attention_rows")
     return out
@@ -1217,10 +1236,12 @@ def biased_paged_attention(qkv: torch.Tensor, pool: torch.Tensor, page_table: to
 
 def paged_softmax_attention(q: torch.Tensor, pool: torch.Tensor, page_table: torch.Tensor, ctx, *, num_heads: int, num_kv_heads: int,
                             key_dim: int, value_dim: int, scale: float, window: int | None = None, sinks: torch.Tensor | None = None,
-                            gate: torch.Tensor | None = None) -> torch.Tensor:
+                            gate: torch.Tensor | None = None, keep_first: int | None = None, chunk: int | None = None,
+                            softcap: float | None = None, slopes: torch.Tensor | None = None) -> torch.Tensor:
     """Grouped-query softmax attention of prepared queries ``q [N, num_heads * key_dim]`` over keys and values in
     ``pool [pages, 2, kv_heads, page_size, D]`` (``D >= key_dim, value_dim``), with an optional sink per head and an
-    optional sigmoid gate on the output (see :func:`attention_rows`).  Returns ``[N, num_heads * value_dim]``."""
+    optional sigmoid gate on the output, a window that may keep the first keys, blocks of positions, a cap on the scores and a
+    distance bias per head (see :func:`attention_rows`).  Returns ``[N, num_heads * value_dim]``."""
     _need(q.dim() == 2 and q.stride(1) == 1 and q.shape[1] == num_heads * key_dim, "paged_softmax_attention: q [N, heads * key_dim]")
     _need(pool.dtype == q.dtype and pool.is_contiguous() and pool.dim() == 5 and tuple(pool.shape[1:3]) == (2, num_kv_heads), "the pool plane does not match the heads")
     page_size, row = pool.shape[3], pool.shape[4]
@@ -1229,7 +1250,8 @@ def paged_softmax_attention(q: torch.Tensor, pool: torch.Tensor, page_table: tor
     head, page = page_size * row, 2 * num_kv_heads * page_size * row
     values = pool.data_ptr() + num_kv_heads * head * pool.element_size()
     out = attention_rows(q3, None, _ptr(pool), (page, head, row), values, (page, head, row), value_dim, page_table, page_size, ctx,
-                         num_heads=num_heads, num_kv_heads=num_kv_heads, scale=scale, window=window, sinks=sinks, gate=gate)
+                         num_heads=num_heads, num_kv_heads=num_kv_heads, scale=scale, window=window, sinks=sinks, gate=gate,
+                         keep_first=keep_first, chunk=chunk, softcap=softcap, slopes=slopes)
     return out.view(q.shape[0], num_heads * value_dim)
 
 
@@ -1237,7 +1259,8 @@ def head_prepare(proj: torch.Tensor, positions: torch.Tensor | None, *, heads: i
                  bias: torch.Tensor | None = None, q_weight: torch.Tensor | None = None, k_weight: torch.Tensor | None = None,
                  eps: float = 0.0, freq: torch.Tensor | None = None, warm: tuple[float, int] | None = None,
                  values_are_keys: bool = False, pool: torch.Tensor | None = None, slot_map: torch.Tensor | None = None,
-                 out_dtype: torch.dtype | None = None) -> torch.Tensor:
+                 out_dtype: torch.dtype | None = None, interleaved: bool = False, values_out: torch.Tensor | None = None,
+                 values_first: torch.Tensor | None = None, values_lambda: float = 0.0) -> torch.Tensor:
     """From a token's stacked projections ``proj`` rows ``[heads x dim | kv_heads x dim | kv_heads x value_dim]`` to
     queries, keys and values, in this order: ``bias`` (float32, laid out like the row) is added; with ``q_weight`` /
     ``k_weight`` (float32 ``[dim]``) every head is RMS-normed over its lanes (``eps`` inside the root) and weighted; with
@@ -1245,6 +1268,9 @@ def head_prepare(proj: torch.Tensor, positions: torch.Tensor | None, *, heads: i
     ``warm = (coef, every)`` queries are multiplied by ``1 + coef * ln(floor((position + 1) / every) + 1)``.  Keys and values
     go to the tokens' slots of ``pool [pages, 2, kv_heads, page_size, D]``; with ``values_are_keys`` there are no value
     columns and a key head's value is that head with its bias, before norm and rotation.  ``kv_heads = 0``: queries only.
+    ``interleaved``: the rotated lanes pair as ``(2i, 2i + 1)``.  ``values_out`` (float32 ``[N, kv_heads * value_dim]``)
+    takes the values as projected, bias included; with ``values_first`` (the same shape: what an earlier layer kept for
+    these tokens) the values become ``(1 - values_lambda) v + values_lambda values_first`` on their way to the pool.
     Returns the queries ``[N, heads * dim]`` in ``out_dtype`` (default: the pool's type)."""
     cols = (heads + kv_heads) * dim + (0 if values_are_keys else kv_heads * value_dim)
     _need(proj.dim() == 2 and proj.stride(1) == 1 and proj.shape[1] >= cols, "head_prepare: proj rows are too short")
@@ -1266,13 +1292,17 @@ def head_prepare(proj: torch.Tensor, positions: torch.Tensor | None, *, heads: i
         _i32(slot_map, "slot_map")
         out_dtype = pool.dtype
     out_dtype = out_dtype or proj.dtype
+    for t in (values_out, values_first):
+        _need(t is None or (kv_heads and not values_are_keys and t.dtype == torch.float32 and t.is_contiguous() and tuple(t.shape) == (n, kv_heads * value_dim)),
+              "head_prepare: the values kept for, or taken from, another layer are float32 [N, kv_heads * value_dim]")
     q = torch.empty((n, heads * dim), dtype=out_dtype, device=proj.device)
     coef, every = (float(warm[0]), int(warm[1])) if warm else (0.0, 0)
     code = _launch(
         "llm_head_prepare", _ptr(proj), _code(proj.dtype), proj.stride(0), _ptr(bias), _ptr(q), q.stride(0), _ptr(pool) if kv_heads else None,
         _code(out_dtype), _ptr(slot_map) if kv_heads else None, pool.shape[3] if kv_heads else 1, pool.shape[4] if kv_heads else dim,
         _ptr(q_weight), _ptr(k_weight), float(eps), int(normed), _ptr(freq), rot, _ptr(positions) if (rot or warm) else None, coef, every,
-        n, heads, kv_heads, dim, value_dim, int(values_are_keys), _stream(),
+        n, heads, kv_heads, dim, value_dim, int(values_are_keys), int(interleaved), _ptr(values_out), _ptr(values_first), float(values_lambda),
+        _stream(),
     )
     _check(code, "head_prepare")
     return q
@@ -1353,9 +1383,11 @@ def gated_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, z: torch.Tenso
 
 
 def expert_gated_act(x: torch.Tensor, experts: int, ff: int, shared_ff: int, limit: float, shared_limit: float, slope: float, *,
-                     weights: torch.Tensor | None = None, ids: torch.Tensor | None = None, table: torch.Tensor | None = None) -> torch.Tensor:
+                     weights: torch.Tensor | None = None, ids: torch.Tensor | None = None, table: torch.Tensor | None = None,
+                     up_shift: float = 1.0) -> torch.Tensor:
     """The activation of gated experts whose products are bounded, times each token's weight of the expert:
-    ``g = min(gate, limit)``, ``u = clamp(up, -limit, limit)``, ``y = g * sigmoid(slope * g) * (u + 1) * weight``.
+    ``g = min(gate, limit)``, ``u = clamp(up, -limit, limit)``, ``y = g * sigmoid(slope * g) * (u + up_shift) * weight``
+    (infinite limits, slope 1 and shift 0: ``silu(gate) * up * weight``).
     ``x [N, experts * 2 ff + 2 shared_ff]``: per expert its gate columns, then its up columns; a shared expert's behind them
     (``shared_limit``).  The weight is ``weights[t, e]`` (float32 ``[N, experts (+ 1)]``) or, from ``ids [N]`` and
     ``table [vocab, top]`` (int32), ``1 / top`` for the experts that the table lists for the token's id, 0 for the others and
@@ -1371,7 +1403,7 @@ def expert_gated_act(x: torch.Tensor, experts: int, ff: int, shared_ff: int, lim
         vocab, top = table.shape
     out = torch.empty((x.shape[0], experts * ff + shared_ff), dtype=x.dtype, device=x.device)
     code = _launch("llm_expert_gated_act", _ptr(x), x.stride(0), _ptr(out), out.stride(0), _code(x.dtype), _ptr(weights), ldw, _ptr(ids),
-                   _ptr(table), top, vocab, x.shape[0], experts, ff, shared_ff, float(limit), float(shared_limit), float(slope), _stream())
+                   _ptr(table), top, vocab, x.shape[0], experts, ff, shared_ff, float(limit), float(shared_limit), float(slope), float(up_shift), _stream())
     _check(code, "expert_gated_act")
     return out
 
@@ -1546,17 +1578,22 @@ def route_topk(z: torch.Tensor, correction: torch.Tensor | None, experts: int, t
 
 
 def route(x: torch.Tensor, w_router: torch.Tensor, correction: torch.Tensor | None, experts: int, top: int, scale: float = 1.0,
-          renormalize: bool = False, shared_gate: bool = False) -> torch.Tensor:
+          renormalize: bool = False, shared_gate: bool = False, bias: torch.Tensor | None = None, shared_one: bool = False) -> torch.Tensor:
     """The router's 32-bit product and :func:`route_topk` in one kernel: ``x [N, K]`` (float32 or bfloat16, read as 32-bit),
     ``w_router [experts (+ 1), K]`` float32 (its last row the shared expert's gate with ``shared_gate``).  A token's sums
-    are added in an order of their own, whatever else the step holds.  Returns ``[N, experts (+ 1)]`` float32."""
+    are added in an order of their own, whatever else the step holds.  ``bias`` (float32 ``[experts]``) is added to the
+    logits before anything else.  ``shared_one``: a last column of ones (a shared expert without a gate; the router has no
+    row for it).  With ``renormalize`` and no correction the weights are the softmax over the chosen logits alone.
+    Returns ``[N, experts (+ 1)]`` float32."""
+    _need(not (shared_gate and shared_one), "route: a shared expert has a gate or the weight one, not both")
+    _need(bias is None or (bias.dtype == torch.float32 and bias.is_contiguous() and bias.numel() == experts), "route: bias is float32 [experts]")
     rows = experts + int(shared_gate)
     _need(x.dim() == 2 and x.stride(1) == 1 and w_router.dtype == torch.float32 and w_router.is_contiguous()
           and tuple(w_router.shape) == (rows, x.shape[1]), "route: x [N, K], w_router float32 [experts (+ 1), K]")
     _need(correction is None or (correction.dtype == torch.float32 and correction.is_contiguous() and correction.numel() == experts), "route: correction is float32 [experts]")
-    out = torch.empty((x.shape[0], rows), dtype=torch.float32, device=x.device)
+    out = torch.empty((x.shape[0], rows + int(shared_one)), dtype=torch.float32, device=x.device)
     code = _launch("llm_router", _ptr(x), _code(x.dtype), x.stride(0), _ptr(w_router), _ptr(correction), _ptr(out), x.shape[0], x.shape[1],
-                   experts, top, float(scale), int(renormalize), int(shared_gate), _stream())
+                   experts, top, float(scale), int(renormalize), 2 if shared_one else int(shared_gate), _ptr(bias), _stream())
     _check(code, "route")
     return out
 
@@ -1608,4 +1645,41 @@ def branch_sum_rmsnorm(pending: BranchSum, resid: torch.Tensor, weight: torch.Te
         add_launches(-1)
         return None
     _check(code, "branch_sum_rmsnorm")
+    return out
+
+
+# ------------------------------------------------------------------------------------------------
+# Operations of layers whose projections pass a short convolution over time, and of norms on a part of a stacked
+# projection (csrc/short_conv.cu, stream_ops.cu).
+def short_conv(u: torch.Tensor, weight: torch.Tensor, states: torch.Tensor | None, state_slots: torch.Tensor, ctx, channels: int | None = None) -> torch.Tensor:
+    """A causal convolution over time on each of the first ``channels`` columns of ``u [N, >= channels]`` (rows may have a
+    pitch): ``y_t = sum_j weight[:, j] * u_(t - taps + 1 + j)`` within every request, ``weight [channels, taps]`` float32.
+    What lies before a request's first row of this step is read from ``states[state_slots[r]]`` (``[slots, taps - 1,
+    channels]`` float32: the last rows that earlier steps brought, zeros at a request's start), which is then moved on
+    to the last ``taps - 1`` rows after this step.  Returns ``y [N, channels]`` float32."""
+    c = int(channels) if channels is not None else weight.shape[0]
+    taps = weight.shape[1]
+    _need(u.dim() == 2 and u.stride(1) == 1 and u.shape[1] >= c, "short_conv: u [N, >= channels]")
+    _need(weight.dtype == torch.float32 and weight.is_contiguous() and weight.shape[0] == c and 1 <= taps <= 16, "short_conv: weight is float32 [channels, taps], taps up to 16")
+    if taps > 1:
+        _need(states is not None and states.dtype == torch.float32 and states.is_contiguous() and tuple(states.shape[1:]) == (taps - 1, c), "short_conv: states [slots, taps - 1, channels] float32")
+    _i32(state_slots, "state_slots")
+    out = torch.empty((u.shape[0], c), dtype=torch.float32, device=u.device)
+    code = _launch("llm_short_conv", _ptr(u), _code(u.dtype), u.stride(0), _ptr(weight), _ptr(states), _ptr(state_slots), _ptr(ctx.token_request),
+                   _ptr(ctx.cu_tokens), _ptr(out), out.stride(0), u.shape[0], ctx.num_requests, c, taps, _stream())
+    _check(code, "short_conv")
+    add_launches(int(taps > 1))
+    return out
+
+
+def row_rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+    """``x / sqrt(mean(x^2) + eps) * weight`` row by row for ``x [N, C]`` whose rows may have a pitch (a run of columns of a
+    stacked projection); statistics in 32-bit; a contiguous ``[N, C]`` in ``out_dtype`` (default: the type of ``x``)."""
+    _need(x.dim() == 2 and x.stride(1) == 1 and weight.dtype == torch.float32 and weight.is_contiguous() and weight.numel() == x.shape[1],
+          "row_rmsnorm: x [N, C] with unit inner stride, weight float32 [C]")
+    out_dtype = out_dtype or x.dtype
+    out = torch.empty(x.shape, dtype=out_dtype, device=x.device)
+    code = _launch("llm_row_rmsnorm", _ptr(x), _code(x.dtype), x.stride(0), _ptr(weight), float(eps), _ptr(out), _code(out_dtype), out.stride(0),
+                   x.shape[0], x.shape[1], _stream())
+    _check(code, "row_rmsnorm")
     return out

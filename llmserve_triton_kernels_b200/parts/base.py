@@ -34,7 +34,9 @@ class TensorSpec:
     """One tensor a part owns: its shape and how a random model fills it."""
 
     shape: tuple[int, ...]  # an extent of -1: any size, known only from the checkpoint (a random model takes ``free_size``)
-    init: str = "normal"  # "normal": N(0, std); "ones_plus_normal": 1 + N(0, std); "zeros"; "distinct:<count>": int32 rows of different ids
+    # "normal": N(0, std); "ones_plus_normal": 1 + N(0, std); "half_plus_normal": 1/2 + N(0, std); "mean_plus_normal":
+    # 1 / (last extent) + N(0, std); "eye_plus_normal"; "zeros"; "distinct:<count>": int32 rows of different ids
+    init: str = "normal"
     optional: bool = False  # absent from a checkpoint without error (e.g. a tied head)
     free_size: int = 16  # what a random model uses for an extent of -1
 
@@ -51,11 +53,15 @@ class PartSpec:
 @dataclass(frozen=True)
 class PagedKVSpec:
     """A mixer that keeps keys and values of ``kv_heads x head_dim`` for every token (``window``
-    None) or for the last ``window`` tokens only."""
+    None) or for the last ``window`` tokens only.  ``keep_first``: with a window, the first so many tokens of a
+    request stay as well.  ``chunk``: a query reads only the keys of its own block of ``chunk`` positions (blocks are
+    counted from position 0), so that nothing in front of the newest block is kept."""
 
     kv_heads: int
     head_dim: int
     window: int | None = None
+    keep_first: int | None = None
+    chunk: int | None = None
 
 
 @dataclass(frozen=True)

@@ -20,8 +20,10 @@ class GatedMLP(FeedForward):
 
     def __init__(self, hidden_size: int, intermediate_size: int, activation: str = "silu", bias: bool = False,
                  tensor_names: dict[str, str] | None = None):
-        """``tensor_names``: local names of the three matrices (default ``gate_proj.weight`` and so on)."""
-        self.names = {"gate": "gate_proj.weight", "up": "up_proj.weight", "down": "down_proj.weight", **(tensor_names or {})}
+        """``tensor_names``: local names of the three matrices (default ``gate_proj.weight`` and so on) and, with
+        ``bias``, of their bias vectors (``gate_bias`` and so on; default ``gate_proj.bias`` ...)."""
+        self.names = {"gate": "gate_proj.weight", "up": "up_proj.weight", "down": "down_proj.weight", "gate_bias": "gate_proj.bias",
+                      "up_bias": "up_proj.bias", "down_bias": "down_proj.bias", **(tensor_names or {})}
         if activation not in _ACTIVATIONS:
             raise ValueError(f"activation {activation!r} is not built; known: {_ACTIVATIONS}")
         self.hidden_size = int(hidden_size)
@@ -41,7 +43,7 @@ class GatedMLP(FeedForward):
             self.names["down"]: TensorSpec((h, i)),
         }
         if self.bias:
-            specs.update({"gate_proj.bias": TensorSpec((i,)), "up_proj.bias": TensorSpec((i,)), "down_proj.bias": TensorSpec((h,))})
+            specs.update({self.names["gate_bias"]: TensorSpec((i,)), self.names["up_bias"]: TensorSpec((i,)), self.names["down_bias"]: TensorSpec((h,))})
         return specs
 
     def bind(self, tensors, dtype, device) -> None:
@@ -49,8 +51,8 @@ class GatedMLP(FeedForward):
         self.w_gate_up = fused.to(device).contiguous()
         self.w_down = tensors[self.names["down"]].to(device=device, dtype=dtype).contiguous()
         if self.bias:
-            self.b_gate_up = torch.cat([tensors["gate_proj.bias"].to(dtype), tensors["up_proj.bias"].to(dtype)]).to(device).contiguous()
-            self.b_down = tensors["down_proj.bias"].to(device=device, dtype=dtype).contiguous()
+            self.b_gate_up = torch.cat([tensors[self.names["gate_bias"]].to(dtype), tensors[self.names["up_bias"]].to(dtype)]).to(device).contiguous()
+            self.b_down = tensors[self.names["down_bias"]].to(device=device, dtype=dtype).contiguous()
 
     accepts_sink = True
 
@@ -247,3 +249,68 @@ class TableRoutedMLP(FeedForward):
 
 
 register_part("feed_forward", "table_routed_mlp", TableRoutedMLP)
+
+
+class RoutedGatedMLP(FeedForward):
+    """A mixture of small gated feed-forward layers ``down_e(silu(gate_e x) * up_e x)`` without biases, of which each token
+    uses ``top``, chosen by a router with a bias:
+
+        z = W_router x + b_router (32-bit)
+        chosen: the ``top`` experts with the largest z; weights: the softmax over the chosen logits alone
+        out = sum over the chosen e of weight_e * expert_e(x)  +  shared(x)
+
+    ``shared_size``: the inner size of an expert of the same form that every token uses with weight one (None: none).
+    Tensors: ``router``, ``router.b``, ``e<i>.gate``, ``e<i>.up``, ``e<i>.down``, ``shared.gate``, ``shared.up``, ``shared.down``.
+    As in :class:`TableRoutedMLP` all experts' gate and up matrices are stacked (the shared expert's last) and the down
+    matrices stand side by side: a step is one kernel for the router (its 32-bit product, the choice and the weights), one
+    product over every expert, one kernel for the activation times the token's weight of each expert's block of columns
+    (0, and nothing read, for an expert the token did not choose), and one product that sums over the experts by itself."""
+
+    graph_safe = True
+    accepts_sink = True
+
+    def __init__(self, hidden_size: int, experts: int, top: int, expert_size: int, shared_size: int | None = None, router_bias: bool = True):
+        if not 1 <= int(top) <= int(experts):
+            raise ValueError(f"a token uses {top} of {experts} experts")
+        self.hidden_size, self.experts, self.top, self.expert_size = int(hidden_size), int(experts), int(top), int(expert_size)
+        self.shared_size = int(shared_size) if shared_size else 0
+        self.router_bias = bool(router_bias)
+        self.w_router = self.b_router = self.w_up = self.w_down = None
+
+    def tensors(self) -> dict[str, TensorSpec]:
+        h, f = self.hidden_size, self.expert_size
+        specs = {"router": TensorSpec((self.experts, h))}
+        if self.router_bias:
+            specs["router.b"] = TensorSpec((self.experts,))
+        for e in range(self.experts):
+            specs[f"e{e}.gate"] = TensorSpec((f, h))
+            specs[f"e{e}.up"] = TensorSpec((f, h))
+            specs[f"e{e}.down"] = TensorSpec((h, f))
+        if self.shared_size:
+            specs["shared.gate"] = TensorSpec((self.shared_size, h))
+            specs["shared.up"] = TensorSpec((self.shared_size, h))
+            specs["shared.down"] = TensorSpec((h, self.shared_size))
+        return specs
+
+    def bind(self, tensors, dtype, device) -> None:
+        names = [f"e{e}." for e in range(self.experts)] + (["shared."] if self.shared_size else [])
+        ups = [tensors[p + k] for p in names for k in ("gate", "up")]
+        self.w_up = torch.cat([t.to(dtype) for t in ups], dim=0).to(device).contiguous()  # [E 2 ff + 2 shared, hidden]
+        self.w_down = torch.cat([tensors[p + "down"].to(dtype) for p in names], dim=1).to(device).contiguous()  # [hidden, E ff + shared]
+        self.w_router = tensors["router"].to(device=device, dtype=torch.float32).contiguous()
+        if self.router_bias:
+            self.b_router = tensors["router.b"].to(device=device, dtype=torch.float32).contiguous()
+
+    def forward(self, x, ctx, sink=None):
+        xt = x.materialize() if isinstance(x, ops.NormedInput) else x
+        weights = ops.route(xt, self.w_router, None, self.experts, self.top, 1.0, True, False, bias=self.b_router, shared_one=self.shared_size > 0)
+        act = ops.expert_gated_act(ops.linear(xt, self.w_up), self.experts, self.expert_size, self.shared_size, float("inf"), float("inf"), 1.0,
+                                   weights=weights, up_shift=0.0)
+        if sink is not None:
+            handed_on = sink.linear(act, self.w_down)
+            if handed_on is not None:
+                return handed_on
+        return ops.linear(act, self.w_down, out_dtype=torch.float32)
+
+
+register_part("feed_forward", "routed_gated_mlp", RoutedGatedMLP)

@@ -16,6 +16,11 @@ values per head (``W_uk c``, ``W_uv c``: one product for all new tokens), which 
 attention over the latents; a step whose requests all start at position 0 (``ctx.fresh_requests``) has no cached rows and
 runs the second part alone.  The concatenated heads are multiplied by ``sigmoid(W_g x)`` before the output
 projection.  Sizes, the softmax scale, the rotary base and the names of the tensors are parameters.
+
+Options: ``query_rank`` r: the queries come through a latent of their own, ``q = W_uq rmsnorm(W_dq x) * w_dq`` with
+``W_dq [r, hidden]``, a norm weight ``[r]`` and ``W_uq [H (dim + rot), r]`` in place of ``W_q``; ``rotary_layout =
+"half"``: the rotated lanes pair as ``(i, i + dims/2)`` instead of ``(2i, 2i + 1)``; ``gate_per_head``: the gate is one
+number a head and token, ``W_g [H, hidden]``.
 """
 
 from __future__ import annotations
@@ -25,7 +30,8 @@ import torch
 from .. import ops
 from .base import Mixer, PagedRowSpec, TensorSpec, register_part
 
-_NAMES = {"q": "q", "down": "dkv", "latent_norm": "dkv.norm", "up_k": "uk", "up_v": "uv", "gate": "g", "out": "o"}
+_NAMES = {"q": "q", "down": "dkv", "latent_norm": "dkv.norm", "up_k": "uk", "up_v": "uv", "gate": "g", "out": "o",
+          "q_down": "dq", "q_norm": "dq.norm", "q_up": "uq"}
 
 
 class LatentAttention(Mixer):
@@ -47,6 +53,9 @@ class LatentAttention(Mixer):
         output_gate: bool = True,
         window: int | None = None,
         tensor_names: dict[str, str] | None = None,
+        query_rank: int | None = None,
+        rotary_layout: str = "interleaved",
+        gate_per_head: bool = False,
     ):
         self.hidden_size, self.num_heads = int(hidden_size), int(num_heads)
         self.head_dim, self.rot_dim, self.value_dim, self.rank = int(head_dim), int(rot_dim), int(value_dim), int(rank)
@@ -57,14 +66,28 @@ class LatentAttention(Mixer):
         if self.rank + self.rot_dim > 640 or self.rank > 512:
             raise ValueError(f"a cached row of {rank} + {rot_dim} lanes is not supported: the attention kernels take rows up to 640 with a latent up to 512")
         self.output_gate = bool(output_gate)
+        self.query_rank = int(query_rank) if query_rank else None
+        if rotary_layout not in ("half", "interleaved"):
+            raise ValueError(f"rotated lanes pair as 'half' or 'interleaved', not {rotary_layout!r}")
+        self.rotary_layout = rotary_layout
+        self.gate_per_head = bool(gate_per_head) and self.output_gate
+        self.w_uq = self.q_weight = None
         self.window = None if window is None else int(window)
         self.names = {**_NAMES, **(tensor_names or {})}
         self.w_in = self.w_uk_t = self.w_uv = self.w_up = self.w_out = self.latent_weight = self.freq = None
 
     def tensors(self) -> dict[str, TensorSpec]:
         H, n = self.num_heads, self.names
+        if self.query_rank:
+            queries = {
+                n["q_down"]: TensorSpec((self.query_rank, self.hidden_size)),
+                n["q_norm"]: TensorSpec((self.query_rank,), init="ones_plus_normal"),
+                n["q_up"]: TensorSpec((H * (self.head_dim + self.rot_dim), self.query_rank)),
+            }
+        else:
+            queries = {n["q"]: TensorSpec((H * (self.head_dim + self.rot_dim), self.hidden_size))}
         specs = {
-            n["q"]: TensorSpec((H * (self.head_dim + self.rot_dim), self.hidden_size)),
+            **queries,
             n["down"]: TensorSpec((self.rank + self.rot_dim, self.hidden_size)),
             n["latent_norm"]: TensorSpec((self.rank,), init="ones_plus_normal"),
             n["up_k"]: TensorSpec((H * self.head_dim, self.rank)),
@@ -72,12 +95,15 @@ class LatentAttention(Mixer):
             n["out"]: TensorSpec((self.hidden_size, H * self.value_dim)),
         }
         if self.output_gate:
-            specs[n["gate"]] = TensorSpec((H * self.value_dim, self.hidden_size))
+            specs[n["gate"]] = TensorSpec((H if self.gate_per_head else H * self.value_dim, self.hidden_size))
         return specs
 
     def bind(self, tensors, dtype, device) -> None:
         H, n = self.num_heads, self.names
-        stacked = [tensors[n["q"]], tensors[n["down"]]] + ([tensors[n["gate"]]] if self.output_gate else [])
+        stacked = [tensors[n["q_down" if self.query_rank else "q"]], tensors[n["down"]]] + ([tensors[n["gate"]]] if self.output_gate else [])
+        if self.query_rank:
+            self.w_uq = tensors[n["q_up"]].to(device=device, dtype=dtype).contiguous()
+            self.q_weight = tensors[n["q_norm"]].to(device=device, dtype=torch.float32).contiguous()
         self.w_in = torch.cat([t.to(dtype) for t in stacked], dim=0).to(device).contiguous()
         # W_uk per head, turned so that it multiplies the query: [H, rank, head_dim]
         self.w_uk_t = tensors[n["up_k"]].to(dtype).view(H, self.head_dim, self.rank).transpose(1, 2).contiguous().to(device)
@@ -94,14 +120,25 @@ class LatentAttention(Mixer):
 
     def forward(self, x, ctx, cache, sink=None):
         H, dim, rot, rank = self.num_heads, self.head_dim, self.rot_dim, self.rank
-        proj = ops.linear(x, self.w_in)  # [N, H (dim | rot) | rank | rot | H vdim]
+        proj = ops.linear(x, self.w_in)  # [N, H (dim | rot) | rank | rot | gate], or [N, query rank | rank | rot | gate]
         two_parts = ops.latent_two_parts(ctx, proj.dtype, dim, rot, rank, self.value_dim)
-        prepared = ops.latent_prepare(
-            proj, ctx.positions, cache.slot_map, cache.pool, self.latent_weight, self.freq, self.norm_eps, H, dim, rot, rank,
-            fresh=two_parts,
-        )
+        halves = self.rotary_layout == "half"
+        if self.query_rank:
+            # the queries' latent is normed (32-bit statistics) and expanded: a product of its own behind the stacked one
+            q_all = ops.linear(ops.row_rmsnorm(proj[:, : self.query_rank], self.q_weight, self.norm_eps), self.w_uq)
+            gate_col = self.query_rank + rank + rot
+            prepared = ops.latent_prepare(
+                proj, ctx.positions, cache.slot_map, cache.pool, self.latent_weight, self.freq, self.norm_eps, H, dim, rot, rank,
+                fresh=two_parts, queries=q_all, kv_col=self.query_rank, halves=halves,
+            )
+        else:
+            q_all, gate_col = proj, H * (dim + rot) + rank + rot
+            prepared = ops.latent_prepare(
+                proj, ctx.positions, cache.slot_map, cache.pool, self.latent_weight, self.freq, self.norm_eps, H, dim, rot, rank,
+                fresh=two_parts, **({"halves": True} if halves else {}),
+            )
         q_rot, fresh = prepared if two_parts else (prepared, None)
-        q_plain = proj.as_strided((proj.shape[0], H, dim), (proj.stride(0), dim + rot, 1), proj.storage_offset())
+        q_plain = q_all.as_strided((q_all.shape[0], H, dim), (q_all.stride(0), dim + rot, 1), q_all.storage_offset())
         if two_parts:
             kv = ops.linear(fresh[:, :rank], self.w_up)  # keys and values of the step's own tokens, head by head
             alone = bool(getattr(ctx, "fresh_requests", False))  # every request starts with this step: no cached rows
@@ -126,12 +163,16 @@ class LatentAttention(Mixer):
             )
             if isinstance(mixed, ops.AttentionParts):
                 # few rows, keys cut over several CTAs: their merge, W_uv and the gate are one kernel
-                gate = proj[:, H * (dim + rot) + rank + rot :] if self.output_gate else None
+                gate = proj[:, gate_col:] if self.output_gate and not self.gate_per_head else None
                 out = ops.merge_project_gate(mixed, self.w_uv, gate)
+                if self.gate_per_head:
+                    out = ops.gate_mul(out.view(out.shape[0], H, self.value_dim), proj[:, gate_col : gate_col + H], "sigmoid", per_head=True)
                 return self._project_out(out, sink)
             heads = ops.head_linear(mixed, self.w_uv)  # [N, H, vdim]
-        if self.output_gate:
-            out = ops.gate_mul(heads, proj[:, H * (dim + rot) + rank + rot :], "sigmoid")
+        if self.gate_per_head:
+            out = ops.gate_mul(heads, proj[:, gate_col : gate_col + H], "sigmoid", per_head=True)
+        elif self.output_gate:
+            out = ops.gate_mul(heads, proj[:, gate_col:], "sigmoid")
         else:
             out = heads.reshape(proj.shape[0], H * self.value_dim)
         return self._project_out(out, sink)

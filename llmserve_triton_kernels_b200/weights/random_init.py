@@ -37,6 +37,10 @@ def random_tensor(name: str, spec: TensorSpec, seed: int, std: float, dtype: tor
         values = values + 1.0
     elif spec.init == "eye_plus_normal":
         values = values + torch.eye(spec.shape[0], spec.shape[1])
+    elif spec.init == "half_plus_normal":  # a mixing weight between two things
+        values = values + 0.5
+    elif spec.init == "mean_plus_normal":  # weights that average over the last extent (the taps of a short convolution)
+        values = values + 1.0 / spec.shape[-1]
     elif spec.init != "normal":
         raise ValueError(f"tensor {name!r} has an unknown init {spec.init!r}")
     return values.to(dtype)

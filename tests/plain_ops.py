@@ -175,7 +175,13 @@ def linear_act(x, w, activation):
     return unary(linear(x, w), activation, inplace=True)
 
 
-def gate_mul(a, b, kind="sigmoid"):
+def gate_mul(a, b, kind="sigmoid", per_head=False):
+    if per_head:
+        b = b.repeat_interleave(a.shape[2], dim=1)
+    return _gate_mul(a, b, kind)
+
+
+def _gate_mul(a, b, kind="sigmoid"):
     n, heads, w = a.shape
     g = b.float()
     g = torch.sigmoid(g) if kind == "sigmoid" else g * torch.sigmoid(g)
@@ -213,7 +219,34 @@ def _rotate_interleaved(x, positions, freq):
     return out
 
 
-def latent_prepare(proj, positions, slot_map, plane, weight, freq, eps, heads, dim, rot, rank, fresh=False):
+def _rotate_halves(x, positions, freq):
+    """x [N, heads, rot]: lanes (i, i + pairs) of the first 2 * len(freq) lanes turn by position * freq[i] (float32 angles)."""
+    pairs = freq.numel()
+    if pairs == 0:
+        return x
+    angle = positions.float()[:, None] * freq.float()[None, :]
+    c, s = angle.cos()[:, None, :], angle.sin()[:, None, :]
+    u, v = x[..., :pairs], x[..., pairs : 2 * pairs]
+    return torch.cat((u * c - v * s, v * c + u * s, x[..., 2 * pairs :]), dim=-1)
+
+
+def latent_prepare(proj, positions, slot_map, plane, weight, freq, eps, heads, dim, rot, rank, fresh=False, queries=None, kv_col=0, halves=False):
+    if queries is not None or halves:
+        n = proj.shape[0]
+        turn = _rotate_halves if halves else _rotate_interleaved
+        q_src = proj if queries is None else queries
+        col = heads * (dim + rot) if queries is None else kv_col
+        q_rot = turn(q_src[:, : heads * (dim + rot)].float().view(n, heads, dim + rot)[..., dim:], positions, freq)
+        latent = proj[:, col : col + rank].float()
+        latent = latent / torch.sqrt(latent.pow(2).mean(-1, keepdim=True) + eps) * weight
+        k_rot = turn(proj[:, col + rank : col + rank + rot].float()[:, None, :], positions, freq)[:, 0]
+        rows = torch.cat((latent, k_rot), dim=-1).to(proj.dtype)
+        plane.view(-1, rank + rot)[slot_map.long()] = rows
+        return (q_rot.to(proj.dtype), rows) if fresh else q_rot.to(proj.dtype)
+    return _latent_prepare(proj, positions, slot_map, plane, weight, freq, eps, heads, dim, rot, rank, fresh)
+
+
+def _latent_prepare(proj, positions, slot_map, plane, weight, freq, eps, heads, dim, rot, rank, fresh=False):
     n = proj.shape[0]
     q = proj[:, : heads * (dim + rot)].float().view(n, heads, dim + rot)
     q_rot = _rotate_interleaved(q[..., dim:], positions, freq).to(proj.dtype)
@@ -248,18 +281,23 @@ def head_linear(x, w):
     return torch.einsum("nhk,hmk->nhm", x.float(), w.float()).to(x.dtype)
 
 
-def _attend(q, k, v, first_pos, scale, window, slopes, sinks=None):
+def _attend(q, k, v, first_pos, scale, window, slopes, sinks=None, keep_first=None, chunk=None, softcap=None):
     """q [T, H, dk], k [n, H, dk], v [n, H, dv] float32; query t stands at position first_pos + t.  ``sinks [H]``: a score
     per head that stands in every row's softmax without a value."""
     n = k.shape[0]
     s = torch.einsum("thd,jhd->htj", q, k) * scale
     pos = torch.arange(first_pos, first_pos + q.shape[0], device=q.device)[:, None]
     j = torch.arange(n, device=q.device)[None, :]
+    if softcap:
+        s = softcap * torch.tanh(s / softcap)
     if slopes is not None:
         s = s - slopes.float()[:, None, None] * (pos - j).float()
     visible = j <= pos
     if window:
-        visible = visible & (j > pos - window)
+        inside = j > pos - window
+        visible = visible & ((inside | (j < keep_first)) if keep_first else inside)
+    if chunk:
+        visible = visible & (torch.div(j, chunk, rounding_mode="floor") == torch.div(pos, chunk, rounding_mode="floor"))
     s = s.masked_fill(~visible[None], float("-inf"))
     if sinks is not None:
         s = torch.cat((s, sinks.float()[:, None, None].expand(-1, s.shape[1], 1)), dim=-1)
@@ -297,7 +335,8 @@ def biased_paged_attention(qkv, pool, page_table, ctx, *, num_heads, num_kv_head
     return out
 
 
-def paged_softmax_attention(q, pool, page_table, ctx, *, num_heads, num_kv_heads, key_dim, value_dim, scale, window=None, sinks=None, gate=None):
+def paged_softmax_attention(q, pool, page_table, ctx, *, num_heads, num_kv_heads, key_dim, value_dim, scale, window=None, sinks=None, gate=None,
+                            keep_first=None, chunk=None, softcap=None, slopes=None):
     H, KV = num_heads, num_kv_heads
     page_size = pool.shape[3]
     out = torch.empty((q.shape[0], H * value_dim), dtype=q.dtype, device=q.device)
@@ -308,7 +347,7 @@ def paged_softmax_attention(q, pool, page_table, ctx, *, num_heads, num_kv_heads
         k = pool[pages, 0].float().permute(0, 2, 1, 3).reshape(-1, KV, pool.shape[4])[:n, :, :key_dim]
         v = pool[pages, 1].float().permute(0, 2, 1, 3).reshape(-1, KV, pool.shape[4])[:n, :, :value_dim]
         k, v = k.repeat_interleave(H // KV, dim=1), v.repeat_interleave(H // KV, dim=1)
-        o = _attend(q[t0:t1].float().view(t1 - t0, H, key_dim), k, v, n - (t1 - t0), scale, window, None, sinks).reshape(t1 - t0, -1)
+        o = _attend(q[t0:t1].float().view(t1 - t0, H, key_dim), k, v, n - (t1 - t0), scale, window, slopes, sinks, keep_first, chunk, softcap).reshape(t1 - t0, -1)
         if gate is not None:
             o = o * torch.sigmoid(gate[t0:t1, : H * value_dim].float())
         out[t0:t1] = o.to(out.dtype)
@@ -316,7 +355,8 @@ def paged_softmax_attention(q, pool, page_table, ctx, *, num_heads, num_kv_heads
 
 
 def head_prepare(proj, positions, *, heads, kv_heads, dim, value_dim=0, bias=None, q_weight=None, k_weight=None, eps=0.0, freq=None,
-                 warm=None, values_are_keys=False, pool=None, slot_map=None, out_dtype=None):
+                 warm=None, values_are_keys=False, pool=None, slot_map=None, out_dtype=None, interleaved=False, values_out=None,
+                 values_first=None, values_lambda=0.0):
     n = proj.shape[0]
     cols = (heads + kv_heads) * dim + (0 if values_are_keys else kv_heads * value_dim)
     row = proj[:, :cols].float()
@@ -335,6 +375,9 @@ def head_prepare(proj, positions, *, heads, kv_heads, dim, value_dim=0, bias=Non
         c, s_ = angle.cos()[:, None, :], angle.sin()[:, None, :]
 
         def turn(x):
+            if interleaved:
+                a, b = x[..., 0 : 2 * half : 2], x[..., 1 : 2 * half : 2]
+                return torch.cat((torch.stack((a * c - b * s_, b * c + a * s_), dim=-1).flatten(-2), x[..., 2 * half :]), dim=-1)
             a, b = x[..., :half], x[..., half : 2 * half]
             return torch.cat((a * c - b * s_, b * c + a * s_, x[..., 2 * half :]), dim=-1)
 
@@ -342,6 +385,10 @@ def head_prepare(proj, positions, *, heads, kv_heads, dim, value_dim=0, bias=Non
     if warm:
         coef, every = warm
         q = q * (1.0 + coef * torch.log(torch.div(positions + 1, every, rounding_mode="floor").float() + 1.0))[:, None, None]
+    if values_out is not None:
+        values_out.copy_(v.reshape(n, -1))
+    if values_first is not None:
+        v = (1.0 - values_lambda) * v + values_lambda * values_first.view(n, kv_heads, value_dim)
     if kv_heads:
         out_dtype = pool.dtype
         page_size = pool.shape[3]
@@ -382,7 +429,7 @@ def gated_scan(q, k, v, z, z_bias, inv_tau, q_scale, states, state_slots, cu_tok
     return out
 
 
-def expert_gated_act(x, experts, ff, shared_ff, limit, shared_limit, slope, *, weights=None, ids=None, table=None):
+def expert_gated_act(x, experts, ff, shared_ff, limit, shared_limit, slope, *, weights=None, ids=None, table=None, up_shift=1.0):
     n = x.shape[0]
     xf = x.float()
     if weights is None:
@@ -396,7 +443,7 @@ def expert_gated_act(x, experts, ff, shared_ff, limit, shared_limit, slope, *, w
         base = e * 2 * ff
         g = xf[:, base : base + width].clamp(max=lim)
         u = xf[:, base + width : base + 2 * width].clamp(min=-lim, max=lim)
-        out[:, e * ff : e * ff + width] = g * torch.sigmoid(slope * g) * (u + 1.0) * weights[:, e : e + 1]
+        out[:, e * ff : e * ff + width] = g * torch.sigmoid(slope * g) * (u + up_shift) * weights[:, e : e + 1]
     return out.to(x.dtype)
 
 
@@ -506,8 +553,32 @@ def route_topk(z, correction, experts, top, scale=1.0, renormalize=False, shared
     return w
 
 
-def route(x, w_router, correction, experts, top, scale=1.0, renormalize=False, shared_gate=False):
-    return route_topk(x.float() @ w_router.float().t(), correction, experts, top, scale, renormalize, shared_gate)
+def route(x, w_router, correction, experts, top, scale=1.0, renormalize=False, shared_gate=False, bias=None, shared_one=False):
+    z = x.float() @ w_router.float().t()
+    if bias is not None:
+        z = torch.cat((z[:, :experts] + bias.float(), z[:, experts:]), dim=1)
+    w = route_topk(z, correction, experts, top, scale, renormalize, shared_gate)
+    return torch.cat((w, torch.ones_like(w[:, :1])), dim=1) if shared_one else w
+
+
+def short_conv(u, weight, states, state_slots, ctx, channels=None):
+    c = int(channels) if channels is not None else weight.shape[0]
+    taps = weight.shape[1]
+    out = torch.empty((u.shape[0], c), dtype=torch.float32, device=u.device)
+    cu, slots = ctx.cu_tokens.tolist(), state_slots.tolist()
+    for r in range(len(cu) - 1):
+        t0, t1 = cu[r], cu[r + 1]
+        rows = u[t0:t1, :c].float()
+        if taps > 1:
+            rows = torch.cat((states[slots[r]], rows), dim=0)
+            states[slots[r]] = rows[rows.shape[0] - (taps - 1) :]
+        out[t0:t1] = sum(weight[:, j].float()[None, :] * rows[j : j + (t1 - t0)] for j in range(taps))
+    return out
+
+
+def row_rmsnorm(x, weight, eps, out_dtype=None):
+    v = x.float()
+    return (v / torch.sqrt(v.pow(2).mean(-1, keepdim=True) + eps) * weight).to(out_dtype or x.dtype)
 
 
 def expert_act_scale(x, weights, experts, ff, activation):
@@ -530,6 +601,8 @@ def branch_sum_rmsnorm(pending, resid, weight, eps, out_dtype):
 
 
 ALL = (
+    "short_conv",
+    "row_rmsnorm",
     "paged_softmax_attention",
     "head_prepare",
     "hyper_mix_norm",

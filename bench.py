@@ -14,7 +14,7 @@ cache of the live requests) to its time; ``points`` holds decode at batch 1 and 
 Peaks come from MEASURED_PEAKS.json beside this file when present, else from an earlier
 measurement on the same pool (and the line says which).
 
-``python bench.py --design nurolorn-small|nurolorn-1b|kafepel-small|kafepel-1b|nudodra-small|nudodra-1b`` prints, instead of the line, prefill and decode
+``python bench.py --design nurolorn-small|nurolorn-1b|kafepel-small|kafepel-1b|nudodra-small|nudodra-1b|tenotar-small|tenotar-1b`` prints, instead of the line, prefill and decode
 throughput of that configuration beside a Llama of equal width, depth and feed-forward size, and the design's kernels against
 their rooflines.
 
@@ -219,12 +219,13 @@ def design_comparison(args) -> int:
     entries = len(arch.plan(dcfg).schedule)
     width, vocab = design["width"], design["vocab"]
     nudodra = design["architecture"] == "Nudodra"
-    if nudodra:  # no dense feed-forward: the twin's has the size of what a token uses (its chosen experts and the shared one)
-        moe = next(x["mlp"] for x in design["layers"] if x.get("mlp"))
+    tenotar = design["architecture"] == "Tenotar"
+    if nudodra or tenotar:  # no dense feed-forward (or one layer's only): the twin's has the size of what a token uses (its chosen experts and the shared one)
+        moe = next(x["mlp"] for x in design["layers"] if x.get("mlp") and x["mlp"].get("kind", "moe") == "moe")
         ff = moe["router"]["top"] * moe["expert"]["ff"] + (moe["shared"]["ff"] if moe.get("shared") else 0)
     else:
         ff = next(x["mlp"]["ff"] for x in design["layers"] if x.get("mlp") and "ff" in x["mlp"])
-    gated = design["architecture"] in ("Kafepel", "Nudodra")  # their feed-forwards have three matrices, like the twin's
+    gated = design["architecture"] in ("Kafepel", "Nudodra", "Tenotar")  # their feed-forwards have three matrices, like the twin's
     twin = {
         "architectures": ["LlamaForCausalLM"], "model_type": "llama", "hidden_act": "silu", "rope_theta": 10000.0, "rms_norm_eps": 1e-5,
         "tie_word_embeddings": False, "vocab_size": vocab, "hidden_size": width, "intermediate_size": ff if gated else (ff * 2 // 3 + 63) // 64 * 64,
@@ -257,6 +258,8 @@ def design_comparison(args) -> int:
     compared = [(args.design, design), ("llama-twin", twin)]
     if nudodra:  # the closest design the engine has: side-by-side mixers and a routed feed-forward at the same sizes
         compared.insert(1, (args.design.replace("nudodra", "kafepel"), dict(PRESETS[args.design.replace("nudodra", "kafepel")])))
+    if tenotar:  # the closest design the engine has: the same softmax attention part and a mixture of gated experts at the same sizes
+        compared.insert(1, (args.design.replace("tenotar", "nudodra"), dict(PRESETS[args.design.replace("tenotar", "nudodra")])))
     for name, cfg_dict in compared:
         a = architecture_of(cfg_dict)
         model = random_model(a.config_class.from_dict(cfg_dict), 0, "bfloat16", device)
@@ -329,8 +332,8 @@ def design_comparison(args) -> int:
 
     bf = torch.bfloat16
     kernels = {}
-    if design["architecture"] in ("Kafepel", "Nudodra"):
-        (_nudodra_kernels if nudodra else _kafepel_kernels)(design, twin, ops, torch, timed, ctx_for, i32, hbm, tensor, device)
+    if design["architecture"] in ("Kafepel", "Nudodra", "Tenotar"):
+        (_tenotar_kernels if tenotar else _nudodra_kernels if nudodra else _kafepel_kernels)(design, twin, ops, torch, timed, ctx_for, i32, hbm, tensor, device)
         out["kernels"] = kernels
         out["peaks"] = {"hbm_gbs": peaks["hbm_gbs"], "bf16_tflops": peaks["bf16_tflops"]}
         print(json.dumps(out, indent=1))
@@ -550,6 +553,122 @@ def _nudodra_kernels(design, twin, ops, torch, timed, ctx_for, i32, hbm, tensor,
         hbm(f"kafepel_expert_act_scale_{label}", us, n * ((top * eff + sff) * 2 + (E * eff + sff) * 2))
 
 
+def _tenotar_kernels(design, twin, ops, torch, timed, ctx_for, i32, hbm, tensor, device) -> None:
+    """The Tenotar design's own kernels, alone, at the preset's sizes: one request of 2,048 prompt tokens, and 8 decoding
+    requests of 2,048 cached tokens; beside each the like kernel of the Nudodra design (the closest one the engine has; for
+    attention through latents the Nurolorn design's form) at the same sizes.  Attention's arithmetic counts the (query, key)
+    pairs that the mask leaves; a decode step's bytes are the cached rows that it leaves."""
+    bf = torch.bfloat16
+    A = next(x["mixer"] for x in design["layers"] if x["type"] == "attention")
+    B = next(x["mixer"] for x in design["layers"] if x["type"] == "attention_2")
+    L = next(x["mixer"] for x in design["layers"] if x["type"] == "latent_attention")
+    moe = next(x["mlp"] for x in design["layers"] if x["mlp"] and x["mlp"]["kind"] == "moe")
+    width = design["width"]
+    H, KV, D, V = A["heads"], A["kv_heads"], A["dim"], A["vdim"]
+    window, keep, chunk, taps = A["mask"]["size"], A["mask"].get("keep_first", 0), B["mask"]["size"], B["conv"]
+
+    def seen(qs, cs, kind):
+        """(query, key) pairs of a step under a mask."""
+        total = 0
+        for q, c in zip(qs, cs):
+            for p in range(c - q, c):
+                if kind == "window":
+                    lo = max(0, p - window + 1)
+                    total += p - lo + 1 + min(keep, lo)
+                elif kind == "latent":
+                    total += min(p + 1, L["mask"]["size"])
+                elif kind == "blocks":
+                    total += p % chunk + 1
+                else:
+                    total += p + 1
+        return total
+
+    for label, qs, cs in (("prefill_2048", [2048], [2048]), ("decode_8x2048", [1] * 8, [2048] * 8)):
+        ctx, table, slots, pages = ctx_for(qs, cs)
+        n = ctx.num_tokens
+        prefill = label.startswith("prefill")
+        pool = torch.randn(pages, 2, KV, 16, max(D, V), device=device).to(bf)
+        q = (torch.randn(n, H * D, device=device) * 0.3).to(bf)
+        slopes = 2.0 ** (-8.0 * torch.arange(1, H + 1, device=device) / H)
+        kw = dict(num_heads=H, num_kv_heads=KV, key_dim=D, value_dim=V, scale=A["scale"])
+
+        def attention(name, kind, like=None, **more):
+            pairs = seen(qs, cs, kind)
+            us = timed(lambda: ops.paged_softmax_attention(q, pool, table, ctx, **kw, **more))
+            work = 2.0 * pairs * H * (D + V) if prefill else pairs * KV * (D + V) * 2 + n * H * (D + V) * 2
+            (tensor if prefill else hbm)(f"{name}_{label}", us, work, like=like)
+
+        attention("window_keep_first_attention", "window", like="sink_attention", window=window, keep_first=keep)
+        attention("block_cap_bias_attention", "blocks", like="sink_attention", chunk=chunk, softcap=B.get("softcap"), slopes=slopes)
+        attention("nudodra_sink_attention", "all", sinks=torch.zeros(H, device=device))
+        # the heads' preparation: biases, norms, neighbouring lanes, values mixed with an earlier layer's; Nudodra's beside it
+        proj = torch.randn(n, (H + KV) * D + KV * V, device=device)
+        freq = torch.rand(A["rot"]["dims"] // 2, device=device)
+        b_in, qw, kw_ = torch.randn((H + KV) * D + KV * V, device=device), torch.ones(D, device=device), torch.ones(D, device=device)
+        first = torch.randn(n, KV * V, device=device)
+        us = timed(lambda: ops.head_prepare(proj, ctx.positions, heads=H, kv_heads=KV, dim=D, value_dim=V, bias=b_in, q_weight=qw, k_weight=kw_,
+                                            eps=1e-6, freq=freq, interleaved=True, values_first=first, values_lambda=0.4, pool=pool, slot_map=slots))
+        hbm(f"head_prepare_mixed_values_{label}", us, n * (((H + KV) * D + 2 * KV * V) * 4 + ((H + KV) * D + KV * V) * 2), like="head_prepare")
+        us = timed(lambda: ops.head_prepare(proj, ctx.positions, heads=H, kv_heads=KV, dim=D, value_dim=V, bias=b_in[: (H + KV) * D], q_weight=qw,
+                                            k_weight=kw_, eps=1e-6, freq=freq, values_are_keys=True, pool=pool, slot_map=slots))
+        hbm(f"nudodra_head_prepare_{label}", us, n * ((H + KV) * D * 4 + (H + 2 * KV) * D * 2))
+        # the short convolution over q, k and v (a streaming kernel: its like is the head norm with a gate, of the same traffic per element)
+        C = (H + KV) * D + KV * V
+        wc = torch.randn(C, taps, device=device)
+        states, sl = torch.zeros(8, taps - 1, C, device=device), i32(list(range(len(qs))))
+        us = timed(lambda: ops.short_conv(proj, wc, states, sl, ctx, channels=C))
+        hbm(f"short_conv_{label}", us, n * C * 8 + 2 * len(qs) * (taps - 1) * C * 4, like="head_norm_gate")
+        o, g2, wn = torch.randn(n, H, V, device=device), torch.randn(n, H * V, device=device), torch.ones(V, device=device)
+        us = timed(lambda: ops.head_norm_gate(o, g2, 1e-6, "silu", bf, weight=wn))
+        hbm(f"nudodra_head_norm_gate_{label}", us, n * H * V * (4 + 4 + 2))
+        # attention through latents: the query latent's norm, the preparation with queries of their own, attention over the cached rows
+        LH, rank, rot, hd, qr = L["heads"], L["kv_rank"], L["rot_dim"], L["dim"], L["q_rank"]
+        lproj = torch.randn(n, qr + rank + rot + LH, device=device).to(bf)
+        wq = torch.ones(qr, device=device)
+        us = timed(lambda: ops.row_rmsnorm(lproj[:, :qr], wq, 1e-6))
+        hbm(f"row_rmsnorm_{label}", us, n * qr * 4, like="rmsnorm")
+        resid, wd = torch.randn(n, width, device=device), torch.ones(width, device=device)
+        us = timed(lambda: ops.rmsnorm(resid, wd, 1e-6, out_dtype=bf))
+        hbm(f"nudodra_rmsnorm_{label}", us, n * width * 6)
+        plane = torch.randn(pages, 16, rank + rot, device=device).to(bf)
+        lq = torch.randn(n, LH * (hd + rot), device=device).to(bf)
+        lw, lf = torch.ones(rank, device=device), torch.rand(L["rot"]["dims"] // 2, device=device)
+        us = timed(lambda: ops.latent_prepare(lproj, ctx.positions, slots, plane, lw, lf, 1e-6, LH, hd, rot, rank, queries=lq, kv_col=qr, halves=True))
+        hbm(f"latent_prepare_{label}", us, n * (LH * rot * 4 + (rank + rot) * 4), like="latent_prepare (the Nurolorn design's form)")
+        stacked = torch.randn(n, LH * (hd + rot) + rank + rot, device=device).to(bf)
+        us = timed(lambda: ops.latent_prepare(stacked, ctx.positions, slots, plane, lw, lf, 1e-6, LH, hd, rot, rank))
+        hbm(f"nurolorn_latent_prepare_{label}", us, n * (LH * rot * 4 + (rank + rot) * 4))
+        q_lat, q_rot = torch.randn(n, LH, rank, device=device).to(bf), torch.randn(n, LH, rot, device=device).to(bf)
+        pairs = seen(qs, cs, "latent")
+        for name, win, count in (("latent_window_attention", L["mask"]["size"], pairs), ("nurolorn_latent_attention", None, seen(qs, cs, "all"))):
+            us = timed(lambda: ops.latent_paged_attention(q_lat, q_rot, plane, table, ctx, rank=rank, scale=L["scale"], window=win))
+            work = 2.0 * count * LH * (2 * rank + rot) if prefill else count * (rank + rot) * 2 + n * LH * (2 * rank + rot) * 2
+            (tensor if prefill else hbm)(f"{name}_{label}", us, work, like=None if win is None else "latent attention without a window (the Nurolorn design's)")
+        heads_out, gates = torch.randn(n, LH, L["vdim"], device=device).to(bf), torch.randn(n, LH, device=device).to(bf)
+        us = timed(lambda: ops.gate_mul(heads_out, gates, "sigmoid", per_head=True))
+        hbm(f"gate_a_head_{label}", us, n * LH * L["vdim"] * 4, like="gate_mul (the same kernel with a gate a lane)")
+        wide_gates = torch.randn(n, LH * L["vdim"], device=device).to(bf)
+        us = timed(lambda: ops.gate_mul(heads_out, wide_gates, "sigmoid"))
+        hbm(f"nurolorn_gate_mul_{label}", us, n * LH * L["vdim"] * 6)
+        # the router with its bias and the experts' activation with the router's weights, beside Nudodra's with the table's
+        E, top, eff, sff = moe["router"]["experts"], moe["router"]["top"], moe["expert"]["ff"], moe["shared"]["ff"]
+        x = torch.randn(n, width, device=device).to(bf)
+        wr, br = torch.randn(E, width, device=device) * 0.1, torch.randn(E, device=device)
+        us = timed(lambda: ops.route(x, wr, None, E, top, 1.0, True, False, bias=br, shared_one=True))
+        hbm(f"router_with_bias_{label}", us, n * width * 2 + E * width * 4 + n * (E + 1) * 4, like="router (the Kafepel design's: the same kernel)")
+        corr = torch.zeros(E, device=device)
+        us = timed(lambda: ops.route(x, wr, corr, E, top, 2.5, False, False))
+        hbm(f"kafepel_router_{label}", us, n * width * 2 + E * width * 4 + n * E * 4)
+        up2 = torch.randn(n, 2 * (E * eff + sff), device=device).to(bf)
+        wts = ops.route(x, wr, None, E, top, 1.0, True, False, bias=br, shared_one=True)
+        us = timed(lambda: ops.expert_gated_act(up2, E, eff, sff, float("inf"), float("inf"), 1.0, weights=wts, up_shift=0.0))
+        hbm(f"expert_gated_act_router_weights_{label}", us, n * ((top * eff + sff) * 4 + (E * eff + sff) * 2), like="expert_gated_act")
+        tab = torch.rand(design["vocab"], E, device=device).argsort(dim=1)[:, :top].to(torch.int32).contiguous()
+        ids = torch.randint(0, design["vocab"], (n,), device=device, dtype=torch.int32)
+        us = timed(lambda: ops.expert_gated_act(up2, E, eff, sff, 7.0, 7.0, 1.702, ids=ids, table=tab))
+        hbm(f"nudodra_expert_gated_act_{label}", us, n * ((top * eff + sff) * 4 + (E * eff + sff) * 2))
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -562,8 +681,9 @@ def main() -> int:
                          "fixed number of pages, with preemption")
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the configuration has (recorded in config)")
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 and 64, the end-to-end run and the kernel table")
-    ap.add_argument("--design", choices=["nurolorn-small", "nurolorn-1b", "kafepel-small", "kafepel-1b", "nudodra-small", "nudodra-1b"], default=None,
-                    help="instead of the one line: prefill and decode throughput of a Nurolorn, Kafepel or Nudodra configuration beside a Llama of "
+    ap.add_argument("--design", choices=["nurolorn-small", "nurolorn-1b", "kafepel-small", "kafepel-1b", "nudodra-small", "nudodra-1b", "tenotar-small",
+                                         "tenotar-1b"], default=None,
+                    help="instead of the one line: prefill and decode throughput of a Nurolorn, Kafepel, Nudodra or Tenotar configuration beside a Llama of "
                          "equal width, depth and feed-forward size, and the design's own kernels against their rooflines")
     ap.add_argument("--sweep", action="store_true",
                     help="instead of the one line: a table of decode steps over batch sizes and context lengths and of prefills over prompt lengths")

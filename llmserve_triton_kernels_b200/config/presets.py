@@ -77,7 +77,29 @@ def _nudodra(width: int, pattern: str, heads: int, kv_heads: int, experts: int, 
     return {"architecture": "Nudodra", "vocab": vocab, "width": width, "streams": streams, "norm": {"eps": 1e-6}, "layers": layers}
 
 
+def _tenotar(width: int, pattern: str, heads: int, kv_heads: int, rank: int, q_rank: int, dense_ff: int, experts: int, top: int, expert_ff: int,
+             shared_ff: int, span: int = 512, vocab: int = 32000) -> dict:
+    """``pattern``: one letter a layer, W attention with a window that keeps the first tokens, C attention behind a short
+    convolution over blocks of positions, L attention through latents.  Heads of 64 lanes, a rotated part of 32; windows and
+    blocks of ``span`` positions; the first layer's feed-forward is dense, the others' a mixture of gated experts."""
+    head = 64
+    kinds = {
+        "W": lambda: {"type": "attention", "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": head, "vdim": head, "scale": head ** -0.5,
+                                                     "mask": {"size": span, "keep_first": 16}, "rot": {"base": 10000.0, "dims": head}, "v_mix": True}},
+        "C": lambda: {"type": "attention_2", "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": head, "vdim": head, "scale": head ** -0.5,
+                                                       "mask": {"size": span}, "conv": 4, "softcap": 30.0, "v_mix": True}},
+        "L": lambda: {"type": "latent_attention", "mixer": {"heads": heads, "dim": head, "rot_dim": 32, "vdim": head, "kv_rank": rank, "q_rank": q_rank,
+                                                            "scale": (head + 32) ** -0.5, "mask": {"size": span}, "rot": {"base": 10000.0, "dims": 32}}},
+    }
+    moe = {"kind": "moe", "router": {"experts": experts, "top": top}, "expert": {"ff": expert_ff}, "shared": {"ff": shared_ff}}
+    layers = [{**kinds[c](), "mlp": {"kind": "dense", "ff": dense_ff} if i == 0 else moe} for i, c in enumerate(pattern)]
+    return {"architecture": "Tenotar", "vocab": vocab, "width": width, "layers": layers, "norm": {"eps": 1e-6}, "logit_scale": 1.0}
+
+
 PRESETS: dict[str, dict] = {
+    # Tenotar at the sizes of the Nudodra and Kafepel presets below (the design has no published sizes)
+    "tenotar-small": _tenotar(1024, "WCLWCLWC", 16, 4, 128, 384, 2816, 16, 2, 512, 1024),
+    "tenotar-1b": _tenotar(2048, "WCLWCLWCLWCL", 32, 8, 256, 768, 5632, 32, 4, 704, 1408),
     # Nudodra at the sizes of the Kafepel presets below (the design has no published sizes)
     "nudodra-small": _nudodra(1024, "PAaPAaPP", 16, 4, 16, 2, 512, 1024),
     "nudodra-1b": _nudodra(2048, "PAaPAaPAaPPA", 32, 8, 32, 4, 704, 1408),

@@ -144,7 +144,7 @@ def latent_attention(h, W, p, m, eps, shared=None):
     q = (cq @ W[p + "uq"].T).view(T, H, D + R)
     down = h @ W[p + "dkv"].T
     c = rms(down[:, :rank], eps, W[p + "dkv.norm"])
-    rot = {"dims": R, "base": m["rot"]["base"]}
+    rot = m["rot"]  # its ``dims`` lanes (those of the rotated part, unless the configuration says fewer) turn
     k_rot = rotate_halves(down[:, None, rank:], rot)  # [T, 1, R]
     q_rot = rotate_halves(q[..., D:], rot)
     k = (c @ W[p + "uk"].T).view(T, H, D)

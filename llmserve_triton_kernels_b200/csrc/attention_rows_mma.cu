@@ -397,7 +397,7 @@ merge_two_parts_kernel(const bf16* __restrict__ o1, long long o1_token, long lon
 __global__ void __launch_bounds__(128)
 merge_project_gate_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, int splits,
                           const bf16* __restrict__ w, const bf16* __restrict__ gate, int ldg, bf16* __restrict__ out, int H,
-                          int dv, int n_out) {
+                          int dv, int n_out, int gate_per_head) {
     extern __shared__ float merged[];  // dv floats, then the splits' weights
     float* weights = merged + dv;
     const int item = blockIdx.x, t = item / H, h = item - t * H, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -434,7 +434,7 @@ merge_project_gate_kernel(const float* __restrict__ part_o, const float* __restr
         acc = warp_sum(acc);
         if (lane == 0) {
             const size_t col = (size_t)h * n_out + e;
-            if (gate) acc *= 1.f / (1.f + expf(-__bfloat162float(gate[(size_t)t * ldg + col])));
+            if (gate) acc *= 1.f / (1.f + expf(-__bfloat162float(gate[(size_t)t * ldg + (gate_per_head ? (size_t)h : col)])));
             out[(size_t)t * H * n_out + col] = __float2bfloat16_rn(acc);
         }
     }
@@ -531,14 +531,15 @@ LLM_EXPORT int llm_attention_rows_mma(const void* q0, long long q0_token, long l
 }
 
 // The partial results of llm_attention_rows_mma with splits > 1 and no out (part_o, part_ml), merged, multiplied per head
-// by w [H, n_out, dv] and by sigmoid(gate [n, H * n_out], row pitch ldg; null: no gate) -> out [n, H * n_out].  dv even.
+// by w [H, n_out, dv] and by sigmoid(gate [n, H * n_out], row pitch ldg; null: no gate; gate_per_head: one number a head,
+// gate [n, H]) -> out [n, H * n_out].  dv even.
 LLM_EXPORT int llm_merge_project_gate(const float* part_o, const float* part_ml, int splits, const void* w, const void* gate,
-                                      int ldg, void* out, int n_tokens, int H, int dv, int n_out, cudaStream_t stream) {
+                                      int ldg, void* out, int n_tokens, int H, int dv, int n_out, int gate_per_head, cudaStream_t stream) {
     if (n_tokens <= 0 || H <= 0) return 0;
     if (splits < 1 || splits > 32 || dv <= 0 || (dv & 1) || n_out <= 0 || ((uintptr_t)w & 3)) return LLM_ERR_BAD_ARGUMENT;
     const size_t smem = (size_t)(dv + 32) * sizeof(float);
     return launch_pdl(merge_project_gate_kernel, dim3((unsigned)(n_tokens * H)), dim3(128), smem, stream, part_o, part_ml, splits,
-                      (const bf16*)w, (const bf16*)gate, ldg, (bf16*)out, H, dv, n_out);
+                      (const bf16*)w, (const bf16*)gate, ldg, (bf16*)out, H, dv, n_out, gate_per_head);
 }
 
 // Two parts of one softmax, each normalised by itself (o [n, H, dv] bfloat16 with token and head strides, stats [n, H, 2] =

@@ -300,7 +300,7 @@ LLM_EXPORT int llm_rope_kv_write(void* qkv, int dtype, int row_stride, const int
 // gated activation: out[t, j] = silu(gate_up[t, j]) * gate_up[t, I + j], in 32-bit
 // ---------------------------------------------------------------------------------------------
 template <typename T>
-__global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, size_t total) {
+__global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, size_t total, const T* __restrict__ bias) {
     pdl_trigger();
     pdl_wait();
     const size_t stride = (size_t)gridDim.x * blockDim.x;
@@ -311,6 +311,13 @@ __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out
             float g[4], u[4];
             load4(gate_up + t * 2 * inter + j, g);
             load4(gate_up + t * 2 * inter + inter + j, u);
+            if (bias) {  // the projections' bias [2 inter], laid out like a row: added in 32-bit on the way in
+                float bg[4], bu[4];
+                load4(bias + j, bg);
+                load4(bias + inter + j, bu);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) { g[e] += bg[e]; u[e] += bu[e]; }
+            }
 #pragma unroll
             for (int e = 0; e < 4; ++e) g[e] = g[e] / (1.f + expf(-g[e])) * u[e];
             store4(out + i, g);
@@ -320,13 +327,13 @@ __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
         const size_t t = i / inter;
         const int j = (int)(i - t * inter);
-        const float g = to_float(gate_up[t * 2 * inter + j]);
-        const float u = to_float(gate_up[t * 2 * inter + inter + j]);
+        const float g = to_float(gate_up[t * 2 * inter + j]) + (bias ? to_float(bias[j]) : 0.f);
+        const float u = to_float(gate_up[t * 2 * inter + inter + j]) + (bias ? to_float(bias[inter + j]) : 0.f);
         out[i] = from_float<T>(g / (1.f + expf(-g)) * u);
     }
 }
 
-LLM_EXPORT int llm_swiglu(const void* gate_up, void* out, int dtype, int n, int inter, cudaStream_t stream) {
+LLM_EXPORT int llm_swiglu(const void* gate_up, void* out, int dtype, int n, int inter, const void* bias, cudaStream_t stream) {
     if (n <= 0) return 0;
     const size_t total = (size_t)n * inter;
     const int threads = 256;
@@ -334,10 +341,10 @@ LLM_EXPORT int llm_swiglu(const void* gate_up, void* out, int dtype, int n, int 
     const size_t most = 148 * 16;  // sixteen blocks an SM of a B200; the kernel's loop strides over what is left
     const int blocks = (int)(want < most ? want : most);
     if (dtype == LLM_F32)
-        return launch_pdl(swiglu_kernel<float>, dim3(blocks), dim3(threads), 0, stream, (const float*)gate_up, (float*)out, inter, total);
+        return launch_pdl(swiglu_kernel<float>, dim3(blocks), dim3(threads), 0, stream, (const float*)gate_up, (float*)out, inter, total, (const float*)bias);
     if (dtype == LLM_BF16)
         return launch_pdl(swiglu_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, (const __nv_bfloat16*)gate_up,
-                          (__nv_bfloat16*)out, inter, total);
+                          (__nv_bfloat16*)out, inter, total, (const __nv_bfloat16*)bias);
     return LLM_ERR_BAD_ARGUMENT;
 }
 

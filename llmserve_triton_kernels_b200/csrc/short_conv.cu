@@ -67,16 +67,60 @@ short_conv_state_kernel(const TI* __restrict__ u, int ldu, float* __restrict__ s
     }
 }
 
+// Steps in which no request brings more than a few tokens (decode steps): one launch.  grid (channel blocks, requests); a
+// thread walks its request's rows for its channel with the last taps - 1 rows in registers, and leaves them in the slot.
+template <typename TI>
+__global__ void __launch_bounds__(128)
+short_conv_walk_kernel(const TI* __restrict__ u, int ldu, const float* __restrict__ w, float* __restrict__ state,
+                       const int* __restrict__ state_slots, const int* __restrict__ cu_tokens, float* __restrict__ y, int ldy, int C, int taps) {
+    pdl_trigger();
+    const int c = blockIdx.x * blockDim.x + threadIdx.x, r = blockIdx.y, back = taps - 1;
+    // taps and rows stand at the END of two arrays of MAX_TAPS (tap j at MAX_TAPS - taps + j, zeros in front), so that every
+    // index is known when the kernel is compiled; a product with a zero tap leaves a sum as it is, bit for bit
+    float wt[MAX_TAPS], hist[MAX_TAPS];
+    const int first = MAX_TAPS - taps;
+    if (c < C)
+#pragma unroll
+        for (int k = 0; k < MAX_TAPS; ++k) wt[k] = k >= first ? w[(size_t)c * taps + (k - first)] : 0.f;
+    const int begin = cu_tokens[r], end = cu_tokens[r + 1];
+    float* slot = state ? state + (size_t)state_slots[r] * back * C : nullptr;
+    pdl_wait();
+    if (c >= C) return;
+#pragma unroll
+    for (int k = 0; k < MAX_TAPS; ++k) hist[k] = k > first ? slot[(size_t)(k - first - 1) * C + c] : 0.f;  // the slot's rows end at the last place
+    for (int t = begin; t < end; ++t) {
+#pragma unroll
+        for (int k = 0; k < MAX_TAPS - 1; ++k) hist[k] = k >= first ? hist[k + 1] : 0.f;  // the oldest row leaves
+        hist[MAX_TAPS - 1] = to_float(u[(size_t)t * ldu + c]);
+        float acc = 0.f;
+#pragma unroll
+        for (int k = 0; k < MAX_TAPS; ++k) acc = fmaf(wt[k], hist[k], acc);  // the oldest row first, as in the other kernel
+        y[(size_t)t * ldy + c] = acc;
+    }
+#pragma unroll
+    for (int k = 0; k < MAX_TAPS; ++k)
+        if (k > first) slot[(size_t)(k - first - 1) * C + c] = hist[k];
+}
+
 }  // namespace
 
 // u [N, >= C] (float32 or bfloat16, row pitch ldu), w [C, taps] float32, state [slots, taps - 1, C] float32,
 // y [N, C] float32 (row pitch ldy).  taps from 1 to 16 (1: a weight a channel, no state).
 LLM_EXPORT int llm_short_conv(const void* u, int dtype, int ldu, const float* w, float* state, const int* state_slots,
                               const int* token_request, const int* cu_tokens, float* y, int ldy, int N, int requests, int C,
-                              int taps, cudaStream_t stream) {
+                              int taps, int max_query_len, cudaStream_t stream) {
     if (N <= 0 || requests <= 0) return 0;
     if (C <= 0 || taps < 1 || taps > MAX_TAPS || ldu < C || ldy < C || (taps > 1 && !state) || requests > 65535) return LLM_ERR_BAD_ARGUMENT;
     constexpr int TOKENS = 8;
+    if (max_query_len > 0 && max_query_len <= 16) {  // few tokens a request: the walk, whose sums have the same order
+        const dim3 wgrid((C + 127) / 128, requests);
+        if (dtype == LLM_F32)
+            return launch_pdl(short_conv_walk_kernel<float>, wgrid, dim3(128), 0, stream, (const float*)u, ldu, w, state, state_slots, cu_tokens, y, ldy, C, taps);
+        if (dtype == LLM_BF16)
+            return launch_pdl(short_conv_walk_kernel<__nv_bfloat16>, wgrid, dim3(128), 0, stream, (const __nv_bfloat16*)u, ldu, w, state, state_slots,
+                              cu_tokens, y, ldy, C, taps);
+        return LLM_ERR_BAD_ARGUMENT;
+    }
     const dim3 block(128), grid((C + 127) / 128, (N + TOKENS - 1) / TOKENS);
     if (grid.y > 65535) return LLM_ERR_UNSUPPORTED;
     int code;

@@ -25,7 +25,7 @@ _SIGNATURES = {
     "llm_embed": [_vp, _vp, _i, _vp, _i, _i, _i, _vp],
     "llm_rmsnorm": [_vp, _vp, _i, _vp, _f, _vp, _vp, _i, _i, _i, _vp],
     "llm_rope_kv_write": [_vp, _i, _i, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
-    "llm_swiglu": [_vp, _vp, _i, _i, _i, _vp],
+    "llm_swiglu": [_vp, _vp, _i, _i, _i, _vp, _vp],
     "llm_add_bias": [_vp, _i, _i, _i, _i, _vp, _vp],
     "llm_fetch_words": [_vp, _vp, _vp, _i, _i, _vp],
     "llm_set_error_flag": [_vp],
@@ -48,7 +48,7 @@ _SIGNATURES = {
     "llm_gate_mul": [_vp, _ll, _ll, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _vp],
     "llm_mingru_scan": [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
     "llm_latent_prepare": [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _f, _i, _i, _i, _i, _i, _i, _vp, _i, _i, _i, _vp],
-    "llm_merge_project_gate": [_vp, _vp, _i, _vp, _vp, _i, _vp, _i, _i, _i, _i, _vp],
+    "llm_merge_project_gate": [_vp, _vp, _i, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _vp],
     "llm_merge_two_parts": [_vp, _ll, _ll, _vp, _vp, _ll, _ll, _vp, _vp, _ll, _ll, _i, _i, _i, _vp],
     "llm_unit_norm_kv_write": [_vp, _i, _i, _vp, _vp, _f, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
     "llm_attention_rows": [_vp, _ll, _ll, _i, _vp, _ll, _ll, _i, _vp, _ll, _ll, _vp, _ll, _ll, _ll, _vp, _ll, _ll, _ll, _i, _i,
@@ -67,7 +67,7 @@ _SIGNATURES = {
     "llm_embed_copies": [_vp, _vp, _i, _vp, _i, _i, _i, _i, _vp],
     "llm_hyper_mix_norm": [_vp, _vp, _vp, _vp, _vp, _f, _f, _f, _f, _i, _vp, _vp, _vp, _vp, _f, _vp, _vp, _i, _i, _i, _i, _i, _vp],
     "llm_head_prepare": [_vp, _i, _i, _vp, _vp, _i, _vp, _i, _vp, _i, _i, _vp, _vp, _f, _i, _vp, _i, _vp, _f, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _f, _vp],
-    "llm_short_conv": [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
+    "llm_short_conv": [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
     "llm_row_rmsnorm": [_vp, _i, _i, _vp, _f, _vp, _i, _i, _i, _i, _vp],
     "llm_gated_scan": [_vp, _i, _vp, _i, _vp, _i, _i, _vp, _i, _vp, _f, _f, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _i, _vp],
     "llm_expert_gated_act": [_vp, _i, _vp, _i, _i, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _f, _f, _f, _vp],
@@ -800,12 +800,14 @@ def _split_counters(device, n: int) -> torch.Tensor:
     return buf
 
 
-def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
-    """``silu(gate_up[:, :I]) * gate_up[:, I:]`` computed in 32-bit -> ``[N, I]``."""
+def swiglu(gate_up: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
+    """``silu(gate_up[:, :I]) * gate_up[:, I:]`` computed in 32-bit -> ``[N, I]``.  ``bias`` (``[2 I]``, of the rows' type,
+    laid out like a row): the two projections' biases, added in 32-bit on the way in."""
     _need(gate_up.dim() == 2 and gate_up.is_contiguous() and gate_up.shape[1] % 2 == 0, "gate_up must be a contiguous [N, 2 I] matrix")
+    _need(bias is None or (bias.dtype == gate_up.dtype and bias.is_contiguous() and bias.numel() == gate_up.shape[1]), "swiglu: the bias is [2 I] of the rows' type")
     n, inter = gate_up.shape[0], gate_up.shape[1] // 2
     out = torch.empty((n, inter), dtype=gate_up.dtype, device=gate_up.device)
-    _check(_launch("llm_swiglu", _ptr(gate_up), _ptr(out), _code(gate_up.dtype), n, inter, _stream()), "swiglu")
+    _check(_launch("llm_swiglu", _ptr(gate_up), _ptr(out), _code(gate_up.dtype), n, inter, _ptr(bias), _stream()), "swiglu")
     return out
 
 
@@ -1147,17 +1149,18 @@ class AttentionParts:
         self.part_o, self.part_ml, self.splits, self.n, self.heads, self.dv = part_o, part_ml, splits, n, heads, dv
 
 
-def merge_project_gate(parts: AttentionParts, w: torch.Tensor, gate: torch.Tensor | None) -> torch.Tensor:
+def merge_project_gate(parts: AttentionParts, w: torch.Tensor, gate: torch.Tensor | None, per_head: bool = False) -> torch.Tensor:
     """``out[t, h * M + e] = sigmoid(gate[t, h * M + e]) * sum_r w[h, e, r] * merged[t, h, r]`` where ``merged`` is what
     :class:`AttentionParts` merge to: the merge, the product per head with ``w [heads, M, dv]`` (bfloat16) and the gate
-    (None: none) in one kernel, for steps of few rows."""
+    (None: none) in one kernel, for steps of few rows.  ``per_head``: one gate a head and token, ``gate [n, heads]``."""
     _need(w.dtype == torch.bfloat16 and w.is_contiguous() and w.dim() == 3 and w.shape[0] == parts.heads and w.shape[2] == parts.dv, "merge_project_gate: w [heads, M, dv] bfloat16")
     m = w.shape[1]
     if gate is not None:
-        _need(gate.dtype == torch.bfloat16 and gate.stride(1) == 1 and tuple(gate.shape) == (parts.n, parts.heads * m), "merge_project_gate: gate [n, heads * M] bfloat16")
+        _need(gate.dtype == torch.bfloat16 and gate.stride(1) == 1 and tuple(gate.shape) == (parts.n, parts.heads if per_head else parts.heads * m),
+              "merge_project_gate: gate [n, heads * M] (or [n, heads]) bfloat16")
     out = torch.empty((parts.n, parts.heads * m), dtype=torch.bfloat16, device=w.device)
     code = _launch("llm_merge_project_gate", _ptr(parts.part_o), _ptr(parts.part_ml), parts.splits, _ptr(w), _ptr(gate),
-                   0 if gate is None else gate.stride(0), _ptr(out), parts.n, parts.heads, parts.dv, m, _stream())
+                   0 if gate is None else gate.stride(0), _ptr(out), parts.n, parts.heads, parts.dv, m, int(per_head), _stream())
     _check(code, "merge_project_gate")
     return out
 
@@ -1656,7 +1659,9 @@ def short_conv(u: torch.Tensor, weight: torch.Tensor, states: torch.Tensor | Non
     pitch): ``y_t = sum_j weight[:, j] * u_(t - taps + 1 + j)`` within every request, ``weight [channels, taps]`` float32.
     What lies before a request's first row of this step is read from ``states[state_slots[r]]`` (``[slots, taps - 1,
     channels]`` float32: the last rows that earlier steps brought, zeros at a request's start), which is then moved on
-    to the last ``taps - 1`` rows after this step.  Returns ``y [N, channels]`` float32."""
+    to the last ``taps - 1`` rows after this step.  A step in which no request brings more than 16 tokens
+    (``ctx.max_query_len``) is one launch that walks every request's rows; the sums have the same order either way.
+    Returns ``y [N, channels]`` float32."""
     c = int(channels) if channels is not None else weight.shape[0]
     taps = weight.shape[1]
     _need(u.dim() == 2 and u.stride(1) == 1 and u.shape[1] >= c, "short_conv: u [N, >= channels]")
@@ -1666,9 +1671,9 @@ def short_conv(u: torch.Tensor, weight: torch.Tensor, states: torch.Tensor | Non
     _i32(state_slots, "state_slots")
     out = torch.empty((u.shape[0], c), dtype=torch.float32, device=u.device)
     code = _launch("llm_short_conv", _ptr(u), _code(u.dtype), u.stride(0), _ptr(weight), _ptr(states), _ptr(state_slots), _ptr(ctx.token_request),
-                   _ptr(ctx.cu_tokens), _ptr(out), out.stride(0), u.shape[0], ctx.num_requests, c, taps, _stream())
+                   _ptr(ctx.cu_tokens), _ptr(out), out.stride(0), u.shape[0], ctx.num_requests, c, taps, int(getattr(ctx, "max_query_len", 0) or 0), _stream())
     _check(code, "short_conv")
-    add_launches(int(taps > 1))
+    add_launches(int(taps > 1 and not 0 < int(getattr(ctx, "max_query_len", 0) or 0) <= 16))
     return out
 
 

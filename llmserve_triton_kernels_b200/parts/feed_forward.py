@@ -58,7 +58,7 @@ class GatedMLP(FeedForward):
 
     def forward(self, x, ctx, sink=None):
         if self.bias:
-            act = ops.swiglu(ops.add_bias(ops.linear(x, self.w_gate_up), self.b_gate_up))
+            act = ops.swiglu(ops.linear(x, self.w_gate_up), self.b_gate_up)  # the bias joins in the activation's kernel
             return ops.add_bias(ops.linear(act, self.w_down, out_dtype=torch.float32), self.b_down.float())
         act = ops.linear_swiglu(x, self.w_gate_up)
         if sink is not None:

@@ -163,10 +163,10 @@ class LatentAttention(Mixer):
             )
             if isinstance(mixed, ops.AttentionParts):
                 # few rows, keys cut over several CTAs: their merge, W_uv and the gate are one kernel
-                gate = proj[:, gate_col:] if self.output_gate and not self.gate_per_head else None
-                out = ops.merge_project_gate(mixed, self.w_uv, gate)
                 if self.gate_per_head:
-                    out = ops.gate_mul(out.view(out.shape[0], H, self.value_dim), proj[:, gate_col : gate_col + H], "sigmoid", per_head=True)
+                    out = ops.merge_project_gate(mixed, self.w_uv, proj[:, gate_col : gate_col + H], per_head=True)
+                else:
+                    out = ops.merge_project_gate(mixed, self.w_uv, proj[:, gate_col:] if self.output_gate else None)
                 return self._project_out(out, sink)
             heads = ops.head_linear(mixed, self.w_uv)  # [N, H, vdim]
         if self.gate_per_head:

@@ -94,9 +94,10 @@ def paged_attention(qkv, pool, page_table, ctx, *, num_heads, num_kv_heads, head
     return out
 
 
-def swiglu(gate_up):
+def swiglu(gate_up, bias=None):
     inter = gate_up.shape[1] // 2
-    g, u = gate_up[:, :inter].float(), gate_up[:, inter:].float()
+    row = gate_up.float() if bias is None else gate_up.float() + bias.float()
+    g, u = row[:, :inter], row[:, inter:]
     return (g * torch.sigmoid(g) * u).to(gate_up.dtype)
 
 

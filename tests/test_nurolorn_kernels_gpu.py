@@ -219,6 +219,9 @@ def test_keys_cut_over_several_ctas_are_merged(ops, dtype):
         ref = plain_ops.gate_mul(plain_ops.head_linear(want, w), gate, "sigmoid")
         close(ops.merge_project_gate(parts, w, gate), ref, dtype, "merge, product per head and gate in one")
         close(ops.merge_project_gate(parts, w, None), plain_ops.head_linear(want, w).reshape(2, -1), dtype, "without a gate")
+        few = rnd(2, heads + 3, dtype=dtype, seed=6)[:, 1 : 1 + heads]  # one gate a head and token
+        ref = plain_ops.gate_mul(plain_ops.head_linear(want, w), few, "sigmoid", per_head=True)
+        close(ops.merge_project_gate(parts, w, few, per_head=True), ref, dtype, "merge, product per head and a gate a head in one")
 
 
 def one_hot_case(ops, dtype, generic, monkeypatch, *, form, context, query_len, target_distance, window, page_size=16):

@@ -242,6 +242,9 @@ def test_row_norm_with_a_pitch_and_a_gate_a_head(dtype, tol):
         w = torch.randn(c, device=DEV)
         for out_dtype in (dtype, torch.float32):
             close(ops.row_rmsnorm(x, w, 1e-5, out_dtype), plain_ops.row_rmsnorm(x, w, 1e-5, out_dtype), tol, f"row norm {n} x {c}")
+    for n, inter in ((1, 1), (5, 36), (130, 7)):  # the feed-forward's biases join in the activation's kernel
+        gate_up, bias = torch.randn(n, 2 * inter, device=DEV).to(dtype), torch.randn(2 * inter, device=DEV).to(dtype)
+        close(ops.swiglu(gate_up, bias), plain_ops.swiglu(gate_up, bias), tol * 2, f"gated activation with biases {n} x {inter}")
     for n, heads, width in ((1, 1, 1), (9, 6, 48), (40, 3, 10)):
         a = torch.randn(n, heads + 1, width + 3, device=DEV).to(dtype)[:, :heads, :width]
         b = torch.randn(n, heads + 5, device=DEV).to(dtype)[:, 2 : 2 + heads]

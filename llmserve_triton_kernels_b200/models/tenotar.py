@@ -72,6 +72,8 @@ def tenotar_plan(cfg: TenotarConfig) -> ModelPlan:
     for i, layer in enumerate(cfg.layers):
         p = f"l{i}."
         parts = {"mixer_norm": PartSpec("rms_norm", {**norm, "weight_name": "norm1"}, p), "mixer": _mixer(cfg, i, layer, p + "mix.")}
+        if layer.type != "latent_attention" and not layer.mixer.get("v_mix"):
+            ignored.append(p + "mix.vmix")  # a checkpoint may carry the mixing weight of a layer that does not mix
         if layer.mlp is None:
             kind = "pre_norm_mixer_only"
             ignored.append(p + "norm2")  # no feed-forward: no use for the norm in front of one

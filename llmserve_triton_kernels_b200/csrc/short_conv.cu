@@ -42,6 +42,65 @@ short_conv_kernel(const TI* __restrict__ u, int ldu, const float* __restrict__ w
     }
 }
 
+// Up to four taps, four neighbouring channels a thread (16-byte loads), `span` tokens a CTA: the rows behind the newest stay in
+// registers from token to token, so that a row is read once (and the taps - 1 rows in front of a CTA's first once more).
+// Taps stand at the end of arrays of four, zeros in front, as in the walk below: the sums have the same order in every kernel.
+template <typename TI>
+__global__ void __launch_bounds__(128)
+short_conv4_kernel(const TI* __restrict__ u, int ldu, const float* __restrict__ w, const float* __restrict__ state,
+                   const int* __restrict__ state_slots, const int* __restrict__ token_request, const int* __restrict__ cu_tokens,
+                   float* __restrict__ y, int ldy, int N, int C, int taps, int span) {
+    constexpr int W = 4;
+    pdl_trigger();
+    const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    const int first = W - taps, back = taps - 1;
+    float wt[W][4];
+    if (c < C)
+#pragma unroll
+        for (int k = 0; k < W; ++k)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) wt[k][e] = k >= first ? w[(size_t)(c + e) * taps + (k - first)] : 0.f;
+    const int t0 = blockIdx.y * span, t1 = min(N, t0 + span);
+    int r = token_request[t0], begin = cu_tokens[r], end = cu_tokens[r + 1];
+    pdl_wait();
+    if (c >= C) return;
+    float hist[W][4];
+    // the rows behind token t: place k holds the row W - 1 - k places behind it, from this step or from the request's slot
+    auto fill = [&](int t) {
+#pragma unroll
+        for (int k = 0; k < W - 1; ++k) {
+            const int src = t - (W - 1 - k);
+            if (k < first) hist[k][0] = hist[k][1] = hist[k][2] = hist[k][3] = 0.f;
+            else if (src >= begin) load4(u + (size_t)src * ldu + c, hist[k]);
+            else load4(state + ((size_t)state_slots[r] * back + (src - begin + back)) * C + c, hist[k]);
+        }
+    };
+    fill(t0);
+    float next[4];
+    load4(u + (size_t)t0 * ldu + c, next);
+    for (int t = t0; t < t1; ++t) {
+        if (t == end) {  // the next request's rows begin: what stands behind them is its own slot
+            ++r;
+            begin = end;
+            end = cu_tokens[r + 1];
+            fill(t);
+        }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) hist[W - 1][e] = next[e];
+        if (t + 1 < t1) load4(u + (size_t)(t + 1) * ldu + c, next);  // on its way while this row is summed
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int k = 0; k < W; ++k)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[e] = fmaf(wt[k][e], hist[k][e], acc[e]);
+        store4(y + (size_t)t * ldy + c, acc);
+#pragma unroll
+        for (int k = 0; k < W - 1; ++k)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) hist[k][e] = k >= first ? hist[k + 1][e] : 0.f;
+    }
+}
+
 // grid (channel blocks, requests): the slot's rows after this step are the last taps - 1 of (old rows, this step's rows)
 template <typename TI>
 __global__ void __launch_bounds__(128)
@@ -122,9 +181,25 @@ LLM_EXPORT int llm_short_conv(const void* u, int dtype, int ldu, const float* w,
         return LLM_ERR_BAD_ARGUMENT;
     }
     const dim3 block(128), grid((C + 127) / 128, (N + TOKENS - 1) / TOKENS);
-    if (grid.y > 65535) return LLM_ERR_UNSUPPORTED;
     int code;
-    if (dtype == LLM_F32)
+    const size_t in_align = dtype == LLM_F32 ? 16 : 8;
+    const bool wide = taps <= 4 && C % 4 == 0 && ldu % 4 == 0 && ldy % 4 == 0 && (uintptr_t)u % in_align == 0 && (uintptr_t)y % 16 == 0 &&
+                      (taps == 1 || (uintptr_t)state % 16 == 0);
+    if (wide) {
+        const int span = N >= 4096 ? 32 : 16;
+        const dim3 g4((C / 4 + 127) / 128, (N + span - 1) / span);
+        if (g4.y > 65535) return LLM_ERR_UNSUPPORTED;
+        if (dtype == LLM_F32)
+            code = launch_pdl(short_conv4_kernel<float>, g4, block, 0, stream, (const float*)u, ldu, w, (const float*)state, state_slots, token_request,
+                              cu_tokens, y, ldy, N, C, taps, span);
+        else if (dtype == LLM_BF16)
+            code = launch_pdl(short_conv4_kernel<__nv_bfloat16>, g4, block, 0, stream, (const __nv_bfloat16*)u, ldu, w, (const float*)state, state_slots,
+                              token_request, cu_tokens, y, ldy, N, C, taps, span);
+        else
+            return LLM_ERR_BAD_ARGUMENT;
+    } else if (grid.y > 65535)
+        return LLM_ERR_UNSUPPORTED;
+    else if (dtype == LLM_F32)
         code = launch_pdl(short_conv_kernel<float, TOKENS>, grid, block, 0, stream, (const float*)u, ldu, w, (const float*)state, state_slots,
                           token_request, cu_tokens, y, ldy, N, C, taps);
     else if (dtype == LLM_BF16)

@@ -16,6 +16,13 @@ from .. import ops
 from .base import Block, FeedForward, Mixer, Norm, register_part
 
 
+def _takes_factored(part) -> bool:
+    """Whether a part reads its input in factored form (``ops.NormedInput``): by default every part that takes a sink for its
+    last product does; one whose first kernel wants the normed rows themselves says ``takes_factored = False`` and gets them
+    from the norm's own kernel."""
+    return bool(getattr(part, "takes_factored", getattr(part, "accepts_sink", False)))
+
+
 class PreNormBlock(Block):
     roles = {"mixer_norm": "norm", "mixer": "mixer", "ff_norm": "norm", "feed_forward": "feed_forward"}
 
@@ -27,8 +34,8 @@ class PreNormBlock(Block):
         self.residual_scale = float(residual_scale)  # x += residual_scale * part(norm(x))
         # whether the part behind each norm takes the stream in factored form (ops.NormedInput); where it does not, the
         # product in front of the norm is not asked for that form (it would only be multiplied out again)
-        mixer_norm.feeds_factored = bool(getattr(mixer, "accepts_sink", False))
-        ff_norm.feeds_factored = bool(getattr(feed_forward, "accepts_sink", False))
+        mixer_norm.feeds_factored = _takes_factored(mixer)
+        ff_norm.feeds_factored = _takes_factored(feed_forward)
 
     @property
     def graph_safe(self) -> bool:
@@ -56,7 +63,7 @@ class PreNormBlock(Block):
         if isinstance(pending, ops.NormedInput):
             if pending.norm is not norm:
                 raise RuntimeError("a part handed the residual stream on normalised for another norm")
-            return pending if getattr(consumer, "accepts_sink", False) else pending.materialize()
+            return pending if _takes_factored(consumer) else pending.materialize()
         if isinstance(pending, ops.BranchSum) and hasattr(norm, "add_branches"):
             x = norm.add_branches(resid, pending)  # the branches' meeting, the sum into the stream and the norm as one kernel
             if x is not None:
@@ -92,7 +99,7 @@ class MixerOnlyBlock(PreNormBlock):
         self.mixer_norm = mixer_norm
         self.mixer = mixer
         self.residual_scale = float(residual_scale)
-        mixer_norm.feeds_factored = bool(getattr(mixer, "accepts_sink", False))
+        mixer_norm.feeds_factored = _takes_factored(mixer)
 
     @property
     def graph_safe(self) -> bool:

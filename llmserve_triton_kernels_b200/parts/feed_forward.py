@@ -268,6 +268,7 @@ class RoutedGatedMLP(FeedForward):
 
     graph_safe = True
     accepts_sink = True
+    takes_factored = False  # the router reads the normed rows themselves: the norm in front runs as its own kernel
 
     def __init__(self, hidden_size: int, experts: int, top: int, expert_size: int, shared_size: int | None = None, router_bias: bool = True):
         if not 1 <= int(top) <= int(experts):

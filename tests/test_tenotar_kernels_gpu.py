@@ -20,7 +20,7 @@ pytestmark = pytest.mark.gpu
 
 # heads, kv heads, key lanes, value lanes, rotated lanes, page size
 SHAPES = [(8, 2, 24, 40, 24, 16), (3, 1, 10, 6, 4, 8), (6, 2, 48, 48, 0, 16), (4, 4, 128, 128, 64, 4), (1, 1, 2, 1, 2, 1), (5, 5, 7, 3, 0, 3),
-          (4, 2, 64, 48, 64, 16), (12, 4, 16, 32, 8, 8)]
+          (4, 2, 64, 32, 64, 16), (12, 4, 16, 32, 8, 8)]
 MASKS = [
     ("a window that keeps the first keys", dict(window=33, keep_first=7)),
     ("more kept keys than the window is wide", dict(window=5, keep_first=70)),
@@ -157,7 +157,7 @@ def test_head_prepare_with_neighbouring_lanes_and_mixed_values(H, KV, D, V, rot,
 
 
 @pytest.mark.parametrize("in_dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("C,taps", [(7, 4), (130, 2), (300, 1), (64, 16), (33, 3)])
+@pytest.mark.parametrize("C,taps", [(7, 4), (130, 2), (300, 1), (64, 16), (33, 3), (64, 4), (132, 3), (8, 2), (520, 1)])
 def test_short_convolution_against_plain_and_across_ways_of_cutting(C, taps, in_dtype):
     """Requests of unequal length in one step against the plain statement (rows with a pitch, slots in any order); then the
     same tokens in portions down to one token through the state slots: bit-equal outputs whatever the cut, and slots that
@@ -166,14 +166,17 @@ def test_short_convolution_against_plain_and_across_ways_of_cutting(C, taps, in_
     torch.manual_seed(C * 10 + taps)
     lens = [70, 1, 19, 33]
     N = sum(lens)
-    u = torch.randn(N, C + 9, device=DEV).to(in_dtype)[:, 2 : 2 + C + 3]
+    if C % 4 == 0 and C != 300:  # rows on 16-byte boundaries with a pitch: the kernel of four channels a thread takes them (up to four taps)
+        u = torch.randn(N, C + 8, device=DEV).to(in_dtype)[:, 4 : 4 + C]
+    else:
+        u = torch.randn(N, C + 9, device=DEV).to(in_dtype)[:, 2 : 2 + C + 3]
     w = torch.randn(C, taps, device=DEV)
     slots = torch.tensor([2, 0, 5, 3], dtype=torch.int32, device=DEV)
 
     def ctx_of(counts):
         cu = torch.tensor([0] + list(itertools.accumulate(counts)), dtype=torch.int32, device=DEV)
         owner = torch.repeat_interleave(torch.arange(len(counts), dtype=torch.int32), torch.tensor(counts)).to(DEV)
-        return SimpleNamespace(cu_tokens=cu, token_request=owner, num_requests=len(counts))
+        return SimpleNamespace(cu_tokens=cu, token_request=owner, num_requests=len(counts), max_query_len=max(counts))
 
     s1 = torch.zeros(6, max(taps - 1, 1), C, device=DEV)[:, : taps - 1]
     s1 = s1.contiguous() if taps > 1 else None
@@ -237,7 +240,7 @@ def test_latent_prepare_with_queries_of_their_own_and_the_half_layout(H, dim, ro
 def test_row_norm_with_a_pitch_and_a_gate_a_head(dtype, tol):
     ops = _ops()
     torch.manual_seed(5)
-    for n, c in ((1, 1), (7, 96), (130, 33), (5, 700)):
+    for n, c in ((1, 1), (7, 88), (130, 33), (5, 700)):
         x = (torch.randn(n, c + 11, device=DEV) * 3).to(dtype)[:, 4 : 4 + c]
         w = torch.randn(c, device=DEV)
         for out_dtype in (dtype, torch.float32):
@@ -245,14 +248,14 @@ def test_row_norm_with_a_pitch_and_a_gate_a_head(dtype, tol):
     for n, inter in ((1, 1), (5, 36), (130, 7)):  # the feed-forward's biases join in the activation's kernel
         gate_up, bias = torch.randn(n, 2 * inter, device=DEV).to(dtype), torch.randn(2 * inter, device=DEV).to(dtype)
         close(ops.swiglu(gate_up, bias), plain_ops.swiglu(gate_up, bias), tol * 2, f"gated activation with biases {n} x {inter}")
-    for n, heads, width in ((1, 1, 1), (9, 6, 48), (40, 3, 10)):
+    for n, heads, width in ((1, 1, 1), (9, 5, 40), (40, 3, 10)):
         a = torch.randn(n, heads + 1, width + 3, device=DEV).to(dtype)[:, :heads, :width]
         b = torch.randn(n, heads + 5, device=DEV).to(dtype)[:, 2 : 2 + heads]
         close(ops.gate_mul(a, b, "sigmoid", per_head=True), plain_ops.gate_mul(a, b, "sigmoid", per_head=True), tol, "a gate a head")
 
 
 @pytest.mark.parametrize("x_dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("N,K,E,top", [(1, 40, 5, 2), (33, 192, 12, 2), (70, 96, 37, 4), (4, 64, 1, 1), (9, 64, 3, 3)])
+@pytest.mark.parametrize("N,K,E,top", [(1, 40, 5, 2), (33, 160, 10, 2), (70, 96, 37, 4), (4, 64, 1, 1), (9, 64, 3, 3)])
 def test_router_with_a_bias_and_gated_experts_against_plain(N, K, E, top, x_dtype):
     ops = _ops()
     torch.manual_seed(N + E)

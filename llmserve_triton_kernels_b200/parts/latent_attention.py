@@ -135,7 +135,7 @@ class LatentAttention(Mixer):
             q_all, gate_col = proj, H * (dim + rot) + rank + rot
             prepared = ops.latent_prepare(
                 proj, ctx.positions, cache.slot_map, cache.pool, self.latent_weight, self.freq, self.norm_eps, H, dim, rot, rank,
-                fresh=two_parts, **({"halves": True} if halves else {}),
+                fresh=two_parts, halves=halves,
             )
         q_rot, fresh = prepared if two_parts else (prepared, None)
         q_plain = q_all.as_strided((q_all.shape[0], H, dim), (q_all.stride(0), dim + rot, 1), q_all.storage_offset())

@@ -159,7 +159,7 @@ attention_rows_mma_kernel(const RowsArgs<bf16> a, int splits, float* __restrict_
         hi[e] = a.key_part == 1 ? min(pos[e], first_pos - 1) : pos[e];
         slope[e] = a.slopes ? a.slopes[kvh * group + R % group] * LOG2E : 0.f;
     }
-    const float scale2 = a.scale * LOG2E, cap2 = a.softcap * LOG2E, cap_in = a.softcap > 0.f ? a.scale / a.softcap : 0.f;
+    const float scale2 = a.scale * LOG2E, cap2 = a.softcap * LOG2E, cap_in2 = a.softcap > 0.f ? 2.f * LOG2E * a.scale / a.softcap : 0.f;
     // the keys that every row of this warp sees: from the newest row's window start to the oldest row's position
     int warp_lo, warp_hi;
     {
@@ -221,7 +221,9 @@ attention_rows_mma_kernel(const RowsArgs<bf16> a, int splits, float* __restrict_
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 const int e = c >> 1, j = j0 + nb * 8 + (lane & 3) * 2 + (c & 1);
-                float v = capped ? cap2 * tanhf(s[nb][c] * cap_in) : s[nb][c] * scale2;
+                // the cap: tanh(t) = 1 - 2 / (e^(2t) + 1), through exp2 and a reciprocal (absolute error near 1e-7, which the cap
+                // multiplies: far below what the bfloat16 operands leave; both ends saturate to +-1)
+                float v = capped ? cap2 * (1.f - __fdividef(2.f, exp2f(s[nb][c] * cap_in2) + 1.f)) : s[nb][c] * scale2;
                 if (biased) v -= slope[e] * (float)(pos[e] - j);
                 if (!whole) v = ((j >= lo[e] || j < kf) && j <= hi[e]) ? v : -INFINITY;
                 s[nb][c] = v;
